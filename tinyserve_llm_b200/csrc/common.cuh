@@ -1,0 +1,90 @@
+// Shared declarations of the kernel library: dtype codes, error reporting, conversions, reductions.
+// Every exported function returns 0 on success; otherwise ts_last_error() holds the reason.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+enum { TS_F32 = 0, TS_BF16 = 1 };
+
+#define TS_API extern "C" __attribute__((visibility("default")))
+
+char* ts_error_buffer();
+
+static inline int ts_fail(const char* fmt, ...) {
+    va_list args;
+    va_start(args, fmt);
+    vsnprintf(ts_error_buffer(), 512, fmt, args);
+    va_end(args);
+    return 1;
+}
+
+#define TS_REQUIRE(cond, ...)                \
+    do {                                     \
+        if (!(cond)) return ts_fail(__VA_ARGS__); \
+    } while (0)
+
+#define TS_LAUNCH_CHECK(name)                                                         \
+    do {                                                                              \
+        cudaError_t e_ = cudaGetLastError();                                          \
+        if (e_ != cudaSuccess) return ts_fail("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
+    } while (0)
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Round to the activation dtype and come back: where the model materialises a tensor.
+template <typename T>
+__device__ __forceinline__ float round_to(float v) { return to_float<T>(from_float<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block in a fixed order (lane tree, then warps in index order): every thread gets it.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < nwarps; ++w) t += scratch[w];
+        scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Geometry of one cache entry inside a layer group's key (or value) pool.  The pool is laid out
+// [page][entry][kv head][token in page][head_dim]; offsets are in elements.
+struct KVGeometry {
+    long long page_stride;    // entries * kv_heads * page_tokens * head_dim
+    long long entry_offset;   // index of the entry in its group * kv_heads * page_tokens * head_dim
+    int page_tokens;
+    int num_pages;
+};

@@ -1,0 +1,29 @@
+// Token embedding: out[t, :] = table[ids[t], :].  Reference op: nn.Embedding (model/llama.py:264,271).
+#include "common.cuh"
+
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
+                                 int hidden, int vocab) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    const bool valid = id >= 0 && id < vocab;      // padding rows carry id -1: they get zeros
+    const T* src = table + (long long)(valid ? id : 0) * hidden;
+    T* dst = out + (long long)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = valid ? src[i] : from_float<T>(0.f);
+}
+
+TS_API int ts_embedding(const void* table, const int* ids, void* out, int num_tokens, int hidden, int vocab,
+                        int dtype, cudaStream_t stream) {
+    TS_REQUIRE(num_tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d", num_tokens, hidden, vocab);
+    if (num_tokens == 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == TS_F32)
+        embedding_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, ids, (float*)out, hidden, vocab);
+    else if (dtype == TS_BF16)
+        embedding_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids,
+                                                                           (__nv_bfloat16*)out, hidden, vocab);
+    else
+        return ts_fail("embedding: unknown dtype code %d", dtype);
+    TS_LAUNCH_CHECK("embedding");
+    return 0;
+}

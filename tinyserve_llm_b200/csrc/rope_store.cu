@@ -1,0 +1,92 @@
+// Rotary position encoding of q and k fused with the write of k and v into the paged cache.
+//
+// Reference: rotate-half with float32 cos/sin gathered by position (model/llama.py:131-136,163-169);
+// keys are stored rotated, values raw, at the slot the block table gives the token's position
+// (engine/model_runner.py:60,100-102; attention/flash_backend.py:22-55).
+//
+// qkv is [T, (nh + 2 nkv) * hd], columns [q | k | v]; q is rotated in place, k and v go to the pool.
+// `table` is [table_rows, rot] float32, cos of the rot/2 angles then their sin; dims >= rot pass
+// through unrotated; a null table stores k unrotated (position applied elsewhere, or none).
+#include "common.cuh"
+
+template <typename T>
+__global__ void rope_store_kernel(T* qkv, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                  const float* __restrict__ table, int rot, const int* __restrict__ block_table,
+                                  int table_width, T* k_pool, T* v_pool, KVGeometry geo, int nh, int nkv, int hd,
+                                  int write_kv) {
+    const int t = blockIdx.x;
+    const int seq = seq_of_token[t];
+    if (seq < 0) return;                                     // padding row
+    const int pos = positions[t];
+    const int row_width = (nh + 2 * nkv) * hd;
+    T* row = qkv + (long long)t * row_width;
+    const float* cs = table ? table + (long long)pos * rot : nullptr;
+    const int half = rot / 2;
+
+    long long base = -1;
+    if (write_kv) {
+        const int page = block_table[(long long)seq * table_width + pos / geo.page_tokens];
+        if (page >= 0 && page < geo.num_pages)
+            base = (long long)page * geo.page_stride + geo.entry_offset + (long long)(pos % geo.page_tokens) * hd;
+    }
+    const long long head_stride = (long long)geo.page_tokens * hd;
+
+    // q and k heads: one thread per (head, pair index or pass-through dim)
+    const int per_head = hd - half;                          // half pairs + (hd - rot) untouched dims
+    const int rotated_heads = nh + nkv;
+    for (int w = threadIdx.x; w < rotated_heads * per_head; w += blockDim.x) {
+        const int head = w / per_head, i = w % per_head;
+        T* h = row + (long long)head * hd;
+        const bool is_k = head >= nh;
+        T* dst = (is_k && base >= 0) ? k_pool + base + (long long)(head - nh) * head_stride : nullptr;
+        if (i < half) {
+            const float x1 = to_float<T>(h[i]), x2 = to_float<T>(h[i + half]);
+            float y1 = x1, y2 = x2;
+            if (cs) {
+                const float c = cs[i], s = cs[half + i];
+                y1 = x1 * c - x2 * s;
+                y2 = x2 * c + x1 * s;
+            }
+            const T o1 = from_float<T>(y1), o2 = from_float<T>(y2);
+            if (!is_k) { h[i] = o1; h[i + half] = o2; }
+            else if (dst) { dst[i] = o1; dst[i + half] = o2; }
+        } else {
+            const int d = rot + (i - half);                  // dims past the rotary part
+            if (is_k && dst) dst[d] = h[d];
+        }
+    }
+    if (base >= 0) {
+        const T* v = row + (long long)(nh + nkv) * hd;
+        for (int w = threadIdx.x; w < nkv * hd; w += blockDim.x) {
+            const int head = w / hd, d = w % hd;
+            v_pool[base + (long long)head * head_stride + d] = v[w];
+        }
+    }
+}
+
+TS_API int ts_rope_store(void* qkv, const int* positions, const int* seq_of_token, const float* table, int table_rows,
+                         int rot, const int* block_table, int table_width, void* k_pool, void* v_pool,
+                         long long page_stride, long long entry_offset, int page_tokens, int num_pages,
+                         int num_tokens, int nh, int nkv, int hd, int write_kv, int dtype, cudaStream_t stream) {
+    TS_REQUIRE(num_tokens >= 0 && nh > 0 && nkv > 0 && hd > 0, "rope_store: bad sizes");
+    TS_REQUIRE(hd % 2 == 0, "rope_store: head_dim %d must be even", hd);
+    if (table) TS_REQUIRE(rot > 0 && rot % 2 == 0 && rot <= hd, "rope_store: rotary width %d does not fit head_dim %d", rot, hd);
+    else rot = 0;
+    TS_REQUIRE(page_tokens > 0 && table_width > 0, "rope_store: bad page geometry");
+    (void)table_rows;
+    if (num_tokens == 0) return 0;
+    KVGeometry geo{page_stride, entry_offset, page_tokens, num_pages};
+    const int threads = 256;
+    if (dtype == TS_F32)
+        rope_store_kernel<float><<<num_tokens, threads, 0, stream>>>((float*)qkv, positions, seq_of_token, table, rot,
+                                                                    block_table, table_width, (float*)k_pool,
+                                                                    (float*)v_pool, geo, nh, nkv, hd, write_kv);
+    else if (dtype == TS_BF16)
+        rope_store_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(
+            (__nv_bfloat16*)qkv, positions, seq_of_token, table, rot, block_table, table_width,
+            (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, geo, nh, nkv, hd, write_kv);
+    else
+        return ts_fail("rope_store: unknown dtype code %d", dtype);
+    TS_LAUNCH_CHECK("rope_store");
+    return 0;
+}

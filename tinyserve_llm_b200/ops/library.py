@@ -1,0 +1,190 @@
+"""
+Python face of the CUDA kernel library: loads the shared object (building it at first use) and
+wraps each exported kernel launcher with argument checks.  There is no CPU fallback and no library
+attention: if the shared object cannot be built or loaded, constructing `Ops` raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from tinyserve_llm_b200.ops.build import build_library
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    """A kernel launcher refused its arguments or the launch failed."""
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class Ops:
+    """One instance per process is enough; see `get_ops()`."""
+
+    def __init__(self, lib_path: str | None = None) -> None:
+        self.lib_path = lib_path or build_library()
+        try:
+            self.lib = ctypes.CDLL(self.lib_path)
+        except OSError as exc:
+            raise KernelError(f"cannot load the CUDA kernel library {self.lib_path}: {exc}") from None
+        self.lib.ts_last_error.restype = ctypes.c_char_p
+        self.lib.ts_abi_version.restype = c_int
+        for name in dir(self.lib):
+            pass
+        self._fast_attention = hasattr(self.lib, "ts_paged_attention_bf16")
+
+    # ------------------------------------------------------------------ helpers
+    def _call(self, name: str, *args) -> None:
+        fn = getattr(self.lib, name)
+        fn.restype = c_int
+        if fn(*args) != 0:
+            raise KernelError(self.lib.ts_last_error().decode())
+
+    @staticmethod
+    def _check(t: torch.Tensor, name: str, dtype: torch.dtype | tuple | None = None, dims: int | None = None) -> None:
+        if not t.is_cuda:
+            raise KernelError(f"{name} must be a CUDA tensor; the engine has no CPU path")
+        if not t.is_contiguous():
+            raise KernelError(f"{name} must be contiguous")
+        if dtype is not None:
+            allowed = dtype if isinstance(dtype, tuple) else (dtype,)
+            if t.dtype not in allowed:
+                raise KernelError(f"{name} has dtype {t.dtype}, expected one of {allowed}")
+        if dims is not None and t.dim() != dims:
+            raise KernelError(f"{name} has {t.dim()} dimensions, expected {dims}")
+
+    # ------------------------------------------------------------------ kernels
+    def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        self._check(table, "embedding table", tuple(_DTYPE_CODE), 2)
+        self._check(ids, "token ids", torch.int32, 1)
+        out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
+        self._call("ts_embedding", _ptr(table), _ptr(ids), _ptr(out), c_int(ids.shape[0]), c_int(table.shape[1]),
+                   c_int(table.shape[0]), c_int(_DTYPE_CODE[table.dtype]), _stream())
+        return out
+
+    def add_rmsnorm(self, x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                    rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+        """
+        (normalised, residual stream).  Without `rows`, both results overwrite their inputs (x and
+        residual) and x starts the stream when residual is None.  With `rows` (int32 row indices)
+        only those rows are normalised into a new compact tensor and the stream is not written.
+        """
+        self._check(x, "x", tuple(_DTYPE_CODE), 2)
+        self._check(weight, "norm weight", tuple(_DTYPE_CODE), 1)
+        hidden = x.shape[1]
+        if weight.shape[0] != hidden:
+            raise KernelError(f"norm weight has {weight.shape[0]} elements for rows of {hidden}")
+        if residual is not None:
+            self._check(residual, "residual", x.dtype, 2)
+            if residual.shape != x.shape:
+                raise KernelError(f"residual {tuple(residual.shape)} does not match x {tuple(x.shape)}")
+        if rows is None:
+            if residual is None:
+                out = torch.empty_like(x)
+                new_residual, residual_out = x, None
+            else:
+                out, new_residual, residual_out = x, residual, residual
+            count = x.shape[0]
+        else:
+            self._check(rows, "rows", torch.int32, 1)
+            count = rows.shape[0]
+            out = torch.empty((count, hidden), dtype=x.dtype, device=x.device)
+            new_residual, residual_out = residual, None
+        self._call("ts_add_rmsnorm", _ptr(x), _ptr(residual), _ptr(weight), _ptr(out), _ptr(residual_out), _ptr(rows),
+                   c_int(count), c_int(hidden), c_float(eps), c_int(_DTYPE_CODE[x.dtype]),
+                   c_int(_DTYPE_CODE[weight.dtype]), _stream())
+        return out, new_residual
+
+    def rope_store(self, qkv: torch.Tensor, ctx, binding, table: torch.Tensor | None, nh: int, nkv: int, hd: int) -> None:
+        self._check(qkv, "qkv", tuple(_DTYPE_CODE), 2)
+        if qkv.shape[1] != (nh + 2 * nkv) * hd:
+            raise KernelError(f"qkv rows have {qkv.shape[1]} columns, expected {(nh + 2 * nkv) * hd}")
+        if binding.k_pool.dtype != qkv.dtype:
+            raise KernelError(f"cache pool is {binding.k_pool.dtype} but activations are {qkv.dtype}")
+        rot, rows = 0, 0
+        if table is not None:
+            self._check(table, "rotary table", torch.float32, 2)
+            rows, rot = table.shape
+        self._call("ts_rope_store", _ptr(qkv), _ptr(ctx.positions), _ptr(ctx.seq_of_token), _ptr(table), c_int(rows),
+                   c_int(rot), _ptr(binding.block_table), c_int(binding.table_width), _ptr(binding.k_pool),
+                   _ptr(binding.v_pool), c_longlong(binding.page_stride), c_longlong(binding.entry_offset),
+                   c_int(binding.page_tokens), c_int(binding.num_pages), c_int(qkv.shape[0]), c_int(nh), c_int(nkv),
+                   c_int(hd), c_int(1 if binding.writes else 0), c_int(_DTYPE_CODE[qkv.dtype]), _stream())
+
+    def paged_attention(self, qkv: torch.Tensor, ctx, binding, nh: int, nkv: int, hd: int, scale: float,
+                        window: int) -> torch.Tensor:
+        self._check(qkv, "qkv", tuple(_DTYPE_CODE), 2)
+        out = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
+        self._call("ts_paged_attention_generic", _ptr(qkv), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
+                   c_longlong(binding.page_stride), c_longlong(binding.entry_offset), c_int(binding.page_tokens),
+                   c_int(binding.num_pages), _ptr(binding.block_table), c_int(binding.table_width),
+                   _ptr(ctx.positions), _ptr(ctx.seq_of_token), c_int(qkv.shape[0]), c_int(nh), c_int(nkv), c_int(hd),
+                   c_float(scale), c_int(window), c_int(_DTYPE_CODE[qkv.dtype]), _stream())
+        return out
+
+    def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:
+        self._check(gate_up, "gate_up", tuple(_DTYPE_CODE), 2)
+        if gate_up.shape[1] % 2:
+            raise KernelError("gate_up rows must hold gate and up halves of equal width")
+        inter = gate_up.shape[1] // 2
+        out = torch.empty((gate_up.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
+        self._call("ts_silu_mul", _ptr(gate_up), _ptr(out), c_int(gate_up.shape[0]), c_int(inter),
+                   c_int(_DTYPE_CODE[gate_up.dtype]), _stream())
+        return out
+
+    def linear(self, x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """x [M, K] . weight[N, K]^T.  float32: the engine's FFMA kernel.  bfloat16: the library product."""
+        self._check(x, "x", tuple(_DTYPE_CODE), 2)
+        self._check(weight, "weight", x.dtype, 2)
+        if x.shape[1] != weight.shape[1]:
+            raise KernelError(f"linear: x has {x.shape[1]} columns, the weight {weight.shape[1]}")
+        if x.dtype == torch.float32:
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
+            self._call("ts_sgemm_nt", _ptr(x), _ptr(weight), _ptr(out), c_int(x.shape[0]), c_int(weight.shape[0]),
+                       c_int(x.shape[1]), c_longlong(x.shape[1]), c_longlong(weight.shape[1]),
+                       c_longlong(weight.shape[0]), _stream())
+            return out
+        if out_dtype is not None and out_dtype != x.dtype:
+            return torch.mm(x, weight.t(), out_dtype=out_dtype)
+        return torch.mm(x, weight.t())
+
+    def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, keys: torch.Tensor) -> torch.Tensor:
+        """int32 [rows]: greedy where temperature is 0, else a draw keyed by keys[row] (two uint32 as int32)."""
+        self._check(logits, "logits", torch.float32, 2)
+        self._check(temperatures, "temperatures", torch.float32, 1)
+        self._check(keys, "keys", torch.int32, 2)
+        rows = logits.shape[0]
+        if temperatures.shape[0] != rows or tuple(keys.shape) != (rows, 2):
+            raise KernelError("sample: one temperature and one key pair per logits row are needed")
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+        self._call("ts_sample", _ptr(logits), c_longlong(logits.shape[1]), _ptr(temperatures), _ptr(keys), _ptr(out),
+                   c_int(rows), c_int(logits.shape[1]), _stream())
+        return out
+
+    def copy_page_slots(self, k_pool: torch.Tensor, v_pool: torch.Tensor, src: int, dst: int, num_slots: int) -> None:
+        """Pools are [pages, entries, kv_heads, page_tokens, head_dim]."""
+        self._check(k_pool, "k_pool", tuple(_DTYPE_CODE), 5)
+        pages, entries, nkv, page_tokens, hd = k_pool.shape
+        self._call("ts_copy_page_slots", _ptr(k_pool), _ptr(v_pool), c_int(pages), c_int(entries), c_int(nkv),
+                   c_int(page_tokens), c_int(hd), c_int(k_pool.dtype.itemsize), c_int(src), c_int(dst),
+                   c_int(num_slots), _stream())
+
+
+_OPS: Ops | None = None
+
+
+def get_ops() -> Ops:
+    global _OPS
+    if _OPS is None:
+        _OPS = Ops()
+    return _OPS
