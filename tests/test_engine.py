@@ -1,0 +1,183 @@
+"""
+The engine through its Python entry point on the GPU: greedy generation equal to the plain
+implementation, unchanged by prefix reuse, portions, preemption and forks; seeded sampling; EOS;
+step records; the command line.
+"""
+
+import json
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama as plain
+import replay_util as ru
+from tiny_configs import PAGE_A, PAGE_B, TINY_A, TINY_B
+
+pytestmark = pytest.mark.gpu
+
+
+def make_llm(folder, page, num_blocks=64, dtype="float32", **kwargs):
+    from tinyserve_llm_b200 import LLM, CacheConfig, SchedulerConfig
+    sched = dict(max_model_len=200, max_num_seqs=8, max_num_batched_tokens=256, eos_token_id=-2, watermark=0.0)
+    sched.update({k: kwargs.pop(k) for k in list(kwargs) if k in SchedulerConfig.__dataclass_fields__})
+    caching = kwargs.pop("caching", True)
+    return LLM(folder, SchedulerConfig(**sched), CacheConfig(block_size=page, caching=caching), dtype=dtype,
+               num_blocks=num_blocks, **kwargs)
+
+
+def greedy(max_tokens=8, **kw):
+    from tinyserve_llm_b200 import SamplingParams
+    return SamplingParams(max_tokens=max_tokens, temperature=0.0, ignore_eos=True, **kw)
+
+
+@pytest.fixture(scope="module")
+def workload_b(model_folders):
+    vocab = TINY_B["vocab_size"]
+    stem = ru.random_ids(vocab, 100, 7)
+    prompts = [stem + ru.random_ids(vocab, 11, 8), ru.random_ids(vocab, 1, 9), stem + ru.random_ids(vocab, 40, 10),
+               ru.random_ids(vocab, 150, 11), stem[:70] + ru.random_ids(vocab, 5, 12), ru.random_ids(vocab, 33, 13)]
+    cfg, tensors = plain.read_model_folder(model_folders["b"])
+    want = [plain.greedy_generate(cfg, tensors, p, 8) for p in prompts]
+    return prompts, want
+
+
+def test_greedy_equals_the_plain_implementation_and_reuses_the_shared_prefix(model_folders, workload_b):
+    prompts, want = workload_b
+    llm = make_llm(model_folders["b"], PAGE_B, prefill_chunk=64, max_num_batched_tokens=96)
+    done = llm.generate(prompts[:1], greedy()) + llm.generate(prompts[1:], greedy())
+    assert [c.token_ids[0] for c in done] == want
+    assert [c.finish_reasons for c in done] == [["length"]] * len(prompts)
+    stats = llm.scheduler.stats()
+    # the first request's pages are found again: 3 whole pages + 4 copied slots, and 2 whole pages + 6 copied slots
+    assert stats.cached_tokens == 100 + 70
+    assert llm.cache.stats().partial_copies == 2
+    assert llm.cache.stats().pages_in_use == 0
+    later = llm.generate([prompts[0]], greedy())     # everything but the last token is cached now
+    assert later[0].token_ids[0] == want[0]
+    assert llm.scheduler.stats().cached_tokens - stats.cached_tokens == len(prompts[0]) - 1
+
+
+@pytest.mark.parametrize("kwargs", [
+    {"caching": False}, {"prefill_chunk": 7, "max_num_batched_tokens": 24}, {"num_blocks": 7, "caching": False},
+    {"step_mode": "prefill_first"}, {"cuda_graphs": False}, {"max_num_seqs": 2}])
+def test_output_does_not_depend_on_how_the_work_is_cut(model_folders, workload_b, kwargs):
+    prompts, want = workload_b
+    llm = make_llm(model_folders["b"], PAGE_B, **kwargs)
+    done = llm.generate(prompts, greedy())
+    assert [c.token_ids[0] for c in done] == want
+    assert llm.cache.stats().pages_in_use == 0
+    if kwargs.get("cuda_graphs", True):
+        assert llm.runner.graph_replays > 0, "decode steps were meant to come from CUDA graphs"
+
+
+@pytest.mark.parametrize("caching", [True, False])
+def test_running_out_of_pages_preempts_and_changes_no_token(model_folders, caching):
+    """Three requests grow from one page to three in a pool of five: a decode finds no page, the lowest score gives way."""
+    vocab = TINY_B["vocab_size"]
+    prompts = [ru.random_ids(vocab, 15, 50 + i) for i in range(3)]
+    cfg, tensors = plain.read_model_folder(model_folders["b"])
+    want = [plain.greedy_generate(cfg, tensors, p, 20) for p in prompts]
+    llm = make_llm(model_folders["b"], 16, num_blocks=5, caching=caching, max_model_len=64)
+    done = llm.generate(prompts, greedy(20))
+    stats = llm.scheduler.stats()
+    assert stats.preemptions > 0 and stats.readmissions > 0
+    assert [c.token_ids[0] for c in done] == want
+    assert llm.cache.stats().pages_in_use == 0
+
+
+def test_bfloat16_generation_stays_with_the_plain_bfloat16_model(model_folders, workload_b):
+    """Token parity is not exact in bfloat16 (near-tied logits); what a token costs in logit is bounded instead."""
+    prompts, _ = workload_b
+    cfg, tensors = plain.read_model_folder(model_folders["b"])
+    llm = make_llm(model_folders["b"], PAGE_B, dtype="bfloat16")
+    done = llm.generate(prompts[:4], greedy(6))
+    for prompt, c in zip(prompts, done):
+        ids = list(prompt)
+        for token in c.token_ids[0]:
+            row = plain.logits(cfg, tensors, ids, "bfloat16")[-1]
+            assert row.max().item() - row[token].item() <= 0.012 * row.abs().max().item() * 2
+            ids.append(token)
+
+
+def test_forks_agree_when_greedy_and_leave_no_page_behind(model_folders):
+    vocab = TINY_A["vocab_size"]
+    prompt = ru.random_ids(vocab, 37, 3)
+    llm = make_llm(model_folders["a"], PAGE_A)
+    done = llm.generate([prompt], greedy(6, n=3))[0]
+    cfg, tensors = plain.read_model_folder(model_folders["a"])
+    assert done.token_ids == [plain.greedy_generate(cfg, tensors, prompt, 6)] * 3
+    assert llm.cache.stats().cow_copies >= 2 and llm.cache.stats().pages_in_use == 0
+
+
+def test_seeded_sampling_is_reproducible_and_independent_of_the_batch(model_folders):
+    from tinyserve_llm_b200 import SamplingParams
+    vocab = TINY_B["vocab_size"]
+    prompts = [ru.random_ids(vocab, n, 20 + n) for n in (9, 40, 77)]
+    params = SamplingParams(max_tokens=10, temperature=0.8, n=2, ignore_eos=True)
+    first = make_llm(model_folders["b"], PAGE_B, seed=5).generate(prompts, params)
+    again = make_llm(model_folders["b"], PAGE_B, seed=5).generate(prompts, params)
+    other = make_llm(model_folders["b"], PAGE_B, seed=6).generate(prompts, params)
+    assert [c.token_ids for c in first] == [c.token_ids for c in again]
+    assert [c.token_ids for c in first] != [c.token_ids for c in other]
+    assert all(c.token_ids[0] != c.token_ids[1] for c in first), "the two samples of a request must differ"
+    # the same request alone, in portions, without graphs: the same draws (keys are per request and position)
+    alone = make_llm(model_folders["b"], PAGE_B, seed=5, prefill_chunk=16, cuda_graphs=False)
+    alone.generate([prompts[2]], greedy(1))                         # takes request id 0; ids key the noise
+    assert alone.generate([prompts[1]], params)[0].token_ids == first[1].token_ids
+
+
+def test_eos_stops_generation_and_is_kept(model_folders):
+    from tinyserve_llm_b200 import SamplingParams
+    prompt = ru.random_ids(TINY_B["vocab_size"], 20, 30)
+    cfg, tensors = plain.read_model_folder(model_folders["b"])
+    free = plain.greedy_generate(cfg, tensors, prompt, 8)
+    stop = free[3]
+    cut = free[:free.index(stop) + 1]
+    llm = make_llm(model_folders["b"], PAGE_B, eos_token_id=stop)
+    done = llm.generate([prompt, prompt], [SamplingParams(max_tokens=8, temperature=0.0),
+                                           SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)])
+    assert done[0].token_ids[0] == cut and done[0].finish_reasons == ["eos"]
+    assert done[1].token_ids[0] == free and done[1].finish_reasons == ["length"]
+    # -1 means: take the model's own end token (the first of config.json's list)
+    assert make_llm(model_folders["b"], PAGE_B, eos_token_id=-1).scheduler.config.eos_token_id == 7
+
+
+def test_step_records_and_requests_the_engine_refuses(model_folders):
+    llm = make_llm(model_folders["a"], PAGE_A)
+    llm.generate([[1, 2, 3, 4, 5]], greedy(3))
+    assert [(r.num_seqs, r.num_tokens) for r in llm.steps] == [(1, 5), (1, 1), (1, 1)]
+    assert llm.steps[-1].scheduler.decode_tokens == 2 and llm.steps[0].end >= llm.steps[0].start
+    with pytest.raises(ValueError, match="vocabulary"):
+        llm.add_request([1, 2, 99999])
+    with pytest.raises(ValueError, match="max_model_len"):
+        llm.add_request([1] * 199, greedy(8))
+    with pytest.raises(ValueError, match="tokenizer"):
+        llm.add_request("some text")
+    with pytest.raises(ValueError, match="max_position_embeddings"):
+        make_llm(model_folders["a"], PAGE_A, max_model_len=100000, max_num_batched_tokens=200000)
+
+
+def test_cache_sized_from_free_memory_and_random_weights_from_a_seed(model_folders):
+    from tinyserve_llm_b200 import LLM, CacheConfig, SchedulerConfig
+    llm = LLM(model_folders["a"], SchedulerConfig(max_model_len=128, max_num_seqs=4, max_num_batched_tokens=128),
+              CacheConfig(block_size=PAGE_A), dtype="bfloat16", gpu_memory_utilization=0.05, random_weights_seed=3)
+    assert llm.cache.num_pages > 100
+    out = llm.generate([[5, 6, 7]], greedy(4))
+    assert len(out[0].token_ids[0]) == 4 and llm.cache.stats().pages_in_use == 0
+
+
+def test_command_line_writes_one_json_record(model_folders, tmp_path):
+    out = tmp_path / "result.json"
+    cmd = [sys.executable, "-m", "tinyserve_llm_b200.cli.generate", "--model", model_folders["a"], "--prompt-ids",
+           "1,2,3,4", "--prompt-ids", "9 8 7", "--max-tokens", "5", "--temperature", "0", "--dtype", "float32",
+           "--block-size", str(PAGE_A), "--num-blocks", "32", "--max-model-len", "128", "--max-num-seqs", "4",
+           "--max-num-batched-tokens", "64", "--ignore-eos", "--out", str(out)]
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=ru.ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    record = json.loads(out.read_text())
+    cfg, tensors = plain.read_model_folder(model_folders["a"])
+    assert [c["token_ids"][0] for c in record["completions"]] == \
+        [plain.greedy_generate(cfg, tensors, p, 5) for p in ([1, 2, 3, 4], [9, 8, 7])]
+    assert record["output_tokens"] == 10 and "output tok/s" in proc.stdout

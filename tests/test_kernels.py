@@ -1,0 +1,264 @@
+"""
+Each CUDA kernel alone against a plain float64 reference of the same operation, at sizes other than
+the tiny models' (widths and vocabularies that are no power of two, head sizes in steps of 16, odd
+groups), with cache pools poisoned with NaN so that a read of a slot nobody wrote shows.
+"""
+
+import math
+
+import pytest
+import torch
+
+import plain_llama as plain
+from gpu_util import DEV, fill_cache, i32, make_binding, make_ctx
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tinyserve_llm_b200.ops import get_ops
+    return get_ops()
+
+
+def act_of(dtype):
+    return "float32" if dtype == torch.float32 else "bfloat16"
+
+
+def tol(dtype, scale=1.0):
+    return dict(atol=2e-6 * scale, rtol=2e-6) if dtype == torch.float32 else dict(atol=1e-2 * scale, rtol=1e-2)
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden, vocab", [(64, 10), (200, 1001), (4104, 37)])
+def test_embedding(ops, dtype, hidden, vocab):
+    table = rand((vocab, hidden), dtype, 1)
+    ids = [0, vocab - 1, 3, 3, -1, vocab // 2]
+    out = ops.embedding(table.to(DEV), i32(ids)).cpu()
+    for row, i in zip(out, ids):
+        assert torch.equal(row, table[i] if i >= 0 else torch.zeros(hidden, dtype=dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden, eps", [(48, 1e-5), (777, 1e-6), (4096, 1e-3), (13000, 1e-5)])
+def test_add_rmsnorm(ops, dtype, hidden, eps):
+    act = act_of(dtype)
+    x, res, w = rand((5, hidden), dtype, 1, 3.0), rand((5, hidden), dtype, 2, 3.0), (1 + rand((hidden,), dtype, 3, 0.3))
+    w = w.to(dtype)
+    want, want_res = plain.add_rms_norm(x.double(), res.double(), w.double(), eps, act)
+    xd, rd = x.to(DEV), res.to(DEV)
+    got, got_res = ops.add_rmsnorm(xd, rd, w.to(DEV), eps)
+    assert got.data_ptr() == xd.data_ptr() and got_res.data_ptr() == rd.data_ptr()      # in place
+    torch.testing.assert_close(got.cpu().double(), want, **tol(dtype, 4))
+    torch.testing.assert_close(got_res.cpu().double(), want_res, **tol(dtype, 8))
+    # no residual: x starts the stream and is left untouched
+    xd = x.to(DEV)
+    got, stream = ops.add_rmsnorm(xd, None, w.to(DEV), eps)
+    assert stream.data_ptr() == xd.data_ptr() and torch.equal(xd.cpu(), x)
+    torch.testing.assert_close(got.cpu().double(), plain.rms_norm(x.double(), w.double(), eps, act), **tol(dtype, 4))
+    # chosen rows only, compact output, inputs untouched
+    xd, rd = x.to(DEV), res.to(DEV)
+    got, _ = ops.add_rmsnorm(xd, rd, w.to(DEV), eps, i32([4, 0, 4]))
+    torch.testing.assert_close(got.cpu().double(), want[[4, 0, 4]], **tol(dtype, 4))
+    assert torch.equal(xd.cpu(), x) and torch.equal(rd.cpu(), res)
+
+
+def test_add_rmsnorm_keeps_a_float32_weight_beside_bfloat16_rows(ops):
+    x, res = rand((3, 96), torch.bfloat16, 1), rand((3, 96), torch.bfloat16, 2)
+    w = 1 + rand((96,), torch.float32, 3, 0.3)
+    s = x.double() + res.double()
+    y = plain.rnd(s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + 1e-5), "bfloat16")
+    want = plain.rnd(y * w.double(), "bfloat16")
+    got, _ = ops.add_rmsnorm(x.to(DEV), res.to(DEV), w.to(DEV), 1e-5)
+    torch.testing.assert_close(got.cpu().double(), want, atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens, inter", [(1, 16), (7, 1000), (130, 5504)])
+def test_silu_mul(ops, dtype, tokens, inter):
+    gu = rand((tokens, 2 * inter), dtype, 4, 2.0)
+    got = ops.silu_mul(gu.to(DEV)).cpu().double()
+    torch.testing.assert_close(got, plain.swiglu(gu.double(), act_of(dtype)), **tol(dtype, 4))
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 1, 1), (3, 130, 70), (65, 64, 17), (200, 1000, 192), (128, 257, 1024)])
+def test_float32_matrix_product(ops, m, n, k):
+    from tinyserve_llm_b200.ops.library import KernelError
+    x, w = rand((m, k), torch.float32, 5), rand((n, k), torch.float32, 6)
+    got = ops.linear(x.to(DEV), w.to(DEV)).cpu().double()
+    torch.testing.assert_close(got, x.double() @ w.double().T, atol=1e-6 * math.sqrt(k) * 4, rtol=1e-6)
+    # a row's result does not depend on the rows beside it
+    alone = ops.linear(x[:1].contiguous().to(DEV), w.to(DEV)).cpu()
+    assert torch.equal(alone[0], ops.linear(x.to(DEV), w.to(DEV)).cpu()[0])
+    with pytest.raises(KernelError):
+        ops.linear(x.to(DEV), rand((n, k + 1), torch.float32, 7).to(DEV))
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 48, 64), (9, 1000, 192), (300, 250, 520)])
+def test_bfloat16_matrix_product(ops, m, n, k):
+    x, w = rand((m, k), torch.bfloat16, 5), rand((n, k), torch.bfloat16, 6)
+    want = x.double() @ w.double().T
+    got = ops.linear(x.to(DEV), w.to(DEV)).cpu().double()
+    torch.testing.assert_close(got, plain.rnd(want, "bfloat16"), atol=2e-2 * math.sqrt(k) / 8, rtol=1e-2)
+    wide = ops.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32).cpu().double()
+    torch.testing.assert_close(wide, want, atol=1e-3 * math.sqrt(k), rtol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh, nkv, hd, rot, page", [(4, 2, 16, 16, 4), (6, 2, 32, 32, 32), (5, 1, 48, 48, 64),
+                                                     (3, 3, 64, 32, 16), (8, 2, 128, 128, 256)])
+def test_rope_store(ops, dtype, nh, nkv, hd, rot, page):
+    """q is rotated in place; k rotated and v raw land in the slots the block table names, nowhere else."""
+    act = act_of(dtype)
+    q_lens, ctx_lens = [3, 1, 5], [3, page + 2, 2 * page + 1]
+    ctx = make_ctx(q_lens, ctx_lens)
+    tables = [[7], [2, 9], [5, 0, 3]]
+    binding = make_binding(10, 2, nkv, page, hd, dtype, tables, entry=1)
+    T = ctx.num_tokens
+    qkv = rand((T, (nh + 2 * nkv) * hd), dtype, 8)
+    g = torch.Generator().manual_seed(9)
+    angles = torch.rand((3 * page + 8, rot // 2), generator=g) * 6.0
+    table = torch.cat((angles.cos(), angles.sin()), dim=-1).float()
+    dev_qkv = qkv.to(DEV)
+    ops.rope_store(dev_qkv, ctx, binding, table.to(DEV), nh, nkv, hd)
+    positions = ctx.positions.cpu().long()
+    cos, sin = table[positions, : rot // 2].double(), table[positions, rot // 2:].double()
+
+    def rotate(x):                                     # [T, heads, hd]; dims past `rot` pass through
+        out = x.double().clone()
+        out[..., :rot] = plain.rotate_half(x.double()[..., :rot], cos, sin, act)
+        return out
+
+    q = qkv[:, : nh * hd].view(T, nh, hd)
+    k = qkv[:, nh * hd: (nh + nkv) * hd].view(T, nkv, hd)
+    v = qkv[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    got_q = dev_qkv.cpu()[:, : nh * hd].view(T, nh, hd).double()
+    torch.testing.assert_close(got_q, rotate(q), **tol(dtype, 4))
+    want_k, expected_slots = rotate(k), set()
+    kp, vp = binding.k_pool.cpu(), binding.v_pool.cpu()
+    for t in range(T):
+        s, pos = int(ctx.seq_of_token[t]), int(positions[t])
+        pg, off = tables[s][pos // page], pos % page
+        expected_slots.add((pg, off))
+        torch.testing.assert_close(kp[pg, 1, :, off].double(), want_k[t], **tol(dtype, 4))
+        assert torch.equal(vp[pg, 1, :, off], v[t])
+    written = {(p, o) for p in range(10) for o in range(page) if not torch.isnan(kp[p, 1, :, o].float()).all()}
+    assert written == expected_slots, "a slot outside the block table was written"
+    assert torch.isnan(kp[:, 0].float()).all(), "the other cache entry of the group was touched"
+
+
+def plain_paged_attention(q, keys, values, ctx_lens, q_lens, scale, window):
+    """q [T, nh, hd] float64; keys/values per sequence [ctx, nkv, hd]: whole-sequence attention, last q_len rows kept."""
+    outs = []
+    start = 0
+    for s, (c, n) in enumerate(zip(ctx_lens, q_lens)):
+        full_q = torch.zeros((c, q.shape[1], q.shape[2]), dtype=torch.float64)
+        full_q[c - n:] = q[start:start + n]
+        outs.append(plain.causal_attention(full_q, keys[s].double(), values[s].double(), scale, "float32", window)[c - n:])
+        start += n
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh, nkv, hd, page, window", [
+    (4, 2, 16, 4, 0), (6, 2, 32, 32, 0), (5, 1, 48, 64, 0), (8, 8, 64, 16, 0), (3, 1, 80, 8, 0),
+    (12, 4, 128, 256, 0), (2, 1, 256, 32, 0), (6, 3, 32, 8, 5), (4, 1, 64, 16, 40)])
+def test_paged_attention(ops, dtype, nh, nkv, hd, page, window):
+    """
+    A whole prompt, a portion over a cached prefix, a decode over a long context and a single first
+    token in one batch, pages scattered and out of order; one score is made to stand out.
+    """
+    q_lens = [page + 3, 7, 1, 1]
+    ctx_lens = [page + 3, 3 * page + 5, 2 * page + 1, 1]
+    ctx = make_ctx(q_lens, ctx_lens)
+    pages_needed = [-(-c // page) for c in ctx_lens]
+    order = torch.randperm(sum(pages_needed) + 3, generator=torch.Generator().manual_seed(3)).tolist()
+    tables, at = [], 0
+    for n in pages_needed:
+        tables.append(order[at:at + n])
+        at += n
+    binding = make_binding(len(order), 1, nkv, page, hd, dtype, tables)
+    keys = [rand((c, nkv, hd), dtype, 20 + s) for s, c in enumerate(ctx_lens)]
+    values = [rand((c, nkv, hd), dtype, 30 + s) for s, c in enumerate(ctx_lens)]
+    T = ctx.num_tokens
+    qkv = rand((T, (nh + 2 * nkv) * hd), dtype, 11)
+    # the decode query of sequence 2 and one far key agree strongly: that key must dominate its row
+    far = 1 if window == 0 else ctx_lens[2] - min(window, ctx_lens[2])
+    row = q_lens[0] + q_lens[1]
+    qkv[row, :hd] = (keys[2][far, 0].float() * 4).to(dtype)
+    for s in range(len(ctx_lens)):
+        fill_cache(binding, s, keys[s], values[s])
+    scale = hd ** -0.5
+    got = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, window).cpu().double().view(T, nh, hd)
+    q = qkv[:, : nh * hd].view(T, nh, hd).double()
+    want = plain_paged_attention(q, keys, values, ctx_lens, q_lens, scale, window)
+    assert torch.isfinite(got).all(), "a slot nobody wrote was read"
+    torch.testing.assert_close(got, plain.rnd(want, act_of(dtype)), **tol(dtype, 2))
+
+
+def test_kernels_refuse_sizes_they_do_not_take(ops):
+    from tinyserve_llm_b200.ops.library import KernelError
+    ctx = make_ctx([1], [1])
+    binding = make_binding(2, 1, 1, 8, 24, torch.float32, [[0]])
+    with pytest.raises(KernelError, match="head_dim 24"):
+        ops.paged_attention(torch.zeros((1, 3 * 24), device=DEV), ctx, binding, 1, 1, 24, 1.0, 0)
+    binding = make_binding(2, 1, 1, 8, 272, torch.float32, [[0]])
+    with pytest.raises(KernelError, match="head_dim 272"):
+        ops.paged_attention(torch.zeros((1, 3 * 272), device=DEV), ctx, binding, 1, 1, 272, 1.0, 0)
+    with pytest.raises(KernelError, match="not a multiple"):
+        ops.paged_attention(torch.zeros((1, 5 * 16), device=DEV), ctx, make_binding(2, 1, 2, 8, 16, torch.float32, [[0]]),
+                            3, 2, 16, 1.0, 0)
+    with pytest.raises(KernelError, match="CUDA tensor"):
+        ops.silu_mul(torch.zeros((2, 8)))
+    with pytest.raises(KernelError, match="contiguous"):
+        ops.silu_mul(torch.zeros((2, 16), device=DEV)[:, ::2])
+
+
+@pytest.mark.parametrize("vocab", [11, 1000, 128256])
+def test_sampling_greedy_and_ties(ops, vocab):
+    logits = rand((4, vocab), torch.float32, 12)
+    logits[1, 5] = logits[1, vocab - 2] = 50.0                     # a tie: the lowest index wins
+    logits[2] = -1e30
+    zeros = torch.zeros(4, dtype=torch.float32, device=DEV)
+    keys = torch.zeros((4, 2), dtype=torch.int32, device=DEV)
+    got = ops.sample(logits.to(DEV), zeros, keys).tolist()
+    want = [int(torch.argmax(r)) for r in logits]
+    want[1], want[2] = 5, 0
+    assert got == want
+
+
+def test_sampling_follows_the_softmax_and_its_keys(ops):
+    from tinyserve_llm_b200.sampling import draw_key
+    vocab, draws, temp = 37, 20000, 0.7
+    row = rand((vocab,), torch.float32, 13, 2.0)
+    logits = row.expand(draws, vocab).contiguous().to(DEV)
+    temps = torch.full((draws,), temp, device=DEV)
+    keys = torch.tensor([draw_key(1, 0, 0, i) for i in range(draws)], dtype=torch.int32, device=DEV)
+    tokens = ops.sample(logits, temps, keys)
+    freq = torch.bincount(tokens.long().cpu(), minlength=vocab).double() / draws
+    assert (freq - plain.sampling_distribution(row, temp)).abs().max() < 0.01
+    assert torch.equal(tokens, ops.sample(logits, temps, keys)), "the same keys must draw the same tokens"
+    shuffled = torch.randperm(draws)
+    again = ops.sample(logits, temps, keys[shuffled.to(DEV)].contiguous())
+    assert torch.equal(again.cpu(), tokens.cpu()[shuffled]), "a draw depends on its key only, not on its row"
+    other = ops.sample(logits, temps, torch.tensor([draw_key(2, 0, 0, i) for i in range(draws)], dtype=torch.int32, device=DEV))
+    assert (other != tokens).float().mean() > 0.5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_copy_page_slots(ops, dtype):
+    shape = (6, 3, 2, 8, 16)
+    k, v = rand(shape, dtype, 14).to(DEV), rand(shape, dtype, 15).to(DEV)
+    k0, v0 = k.clone(), v.clone()
+    ops.copy_page_slots(k, v, 4, 1, 5)
+    assert torch.equal(k[1, :, :, :5], k0[4, :, :, :5]) and torch.equal(v[1, :, :, :5], v0[4, :, :, :5])
+    assert torch.equal(k[1, :, :, 5:], k0[1, :, :, 5:]) and torch.equal(v[1, :, :, 5:], v0[1, :, :, 5:])
+    keep = [0, 2, 3, 4, 5]
+    assert torch.equal(k[keep], k0[keep]) and torch.equal(v[keep], v0[keep])

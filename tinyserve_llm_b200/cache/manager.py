@@ -48,6 +48,7 @@ class CacheLayout:
     groups: tuple[GroupLayout, ...]
     state_offsets: tuple[int, ...]    # per cache entry: byte offset of its state inside a slot, -1 if none
     state_bytes: int                  # bytes of one request's state slot (0: no entry keeps state)
+    state_sizes: tuple[int, ...] = ()  # per cache entry: bytes of its state (0 if none)
 
     @property
     def prefix_reuse_possible(self) -> bool:
@@ -70,6 +71,7 @@ def plan_layout(needs: Sequence[tuple[object | None, int]], page_tokens: int) ->
         raise ValueError(f"page size must be positive, got {page_tokens}")
     by_geometry: dict[tuple[int, int, int], list[int]] = {}
     offsets, total = [], 0
+    sizes = tuple(int(state) for _, state in needs)
     for e, (kv, state) in enumerate(needs):
         if kv is not None:
             by_geometry.setdefault((kv.num_kv_heads, kv.head_dim, kv.window), []).append(e)
@@ -79,7 +81,7 @@ def plan_layout(needs: Sequence[tuple[object | None, int]], page_tokens: int) ->
         else:
             offsets.append(-1)
     groups = tuple(GroupLayout(tuple(es), nkv, hd, w) for (nkv, hd, w), es in by_geometry.items())
-    return CacheLayout(page_tokens, groups, tuple(offsets), total)
+    return CacheLayout(page_tokens, groups, tuple(offsets), total, sizes)
 
 
 class Storage(Protocol):
@@ -379,6 +381,8 @@ class CacheManager:
         """
         seq = self.seqs[seq_id]
         assert 0 <= num_accepted <= seq.reserved - seq.committed, "more slots accepted than reserved"
+        assert not self.layout.state_bytes or num_accepted == seq.reserved - seq.committed, \
+            "a model with per-request state cannot take back tokens it has run"
         B = self.page_tokens
         before = seq.committed
         seq.committed += num_accepted

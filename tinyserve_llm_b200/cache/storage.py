@@ -73,9 +73,9 @@ class DeviceCacheStorage:
                                    self.layout.page_tokens, self.num_pages[g], group=g)
         offset = self.layout.state_offsets[entry] if entry < len(self.layout.state_offsets) else -1
         if offset >= 0:
-            nxt = [o for o in self.layout.state_offsets if o > offset]
-            end = min(nxt) if nxt else self.layout.state_bytes
-            view = self.state[:, offset:end]
+            sizes = self.layout.state_sizes
+            size = sizes[entry] if entry < len(sizes) and sizes[entry] else self.layout.state_bytes - offset
+            view = self.state[:, offset:offset + size]
             if binding is None:
                 binding = EntryBinding(None, None, 0, 0, self.layout.page_tokens, 0, group=-1)
             binding.state = view

@@ -1,0 +1,219 @@
+"""
+The Python entry point: LLM(model_path).generate(prompts, SamplingParams(...)).
+
+Names and meanings of the options follow tinyserve-llm (engine/llm_engine.py:66-185,
+engine/interface.py:28-32): SchedulerConfig, CacheConfig(block_size, caching, device), dtype,
+num_blocks (None: sized from free device memory after a warm-up step), gpu_memory_utilization, seed,
+load_tokenizer; add_request / step / generate; Completion and StepRecord.  There is no `attention`
+option: the engine has one attention implementation, its own kernels.
+"""
+
+from __future__ import annotations
+
+import logging
+import os
+import time
+from dataclasses import dataclass, replace
+
+import torch
+
+from tinyserve_llm_b200.cache.manager import CacheStats, plan_layout
+from tinyserve_llm_b200.cache.storage import DeviceCacheStorage
+from tinyserve_llm_b200.engine.loading import build_cache, load_model, require_cuda, resolve_dtype
+from tinyserve_llm_b200.engine.scheduler import RequestOutput, ScheduledSeq, Scheduler, SchedulerConfig, SchedulerStats
+from tinyserve_llm_b200.engine.sequence import SamplingParams
+from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
+from tinyserve_llm_b200.sampling.sampler import Sampler
+
+logger = logging.getLogger(__name__)
+
+
+@dataclass(frozen=True)
+class CacheConfig:
+    block_size: int = 256        # tokens per cache page
+    caching: bool = True         # False turns prefix reuse off; forks still share pages
+    device: str = "cuda"
+
+
+@dataclass
+class StepRecord:
+    """One engine step; the two stats are running totals (subtract consecutive records)."""
+
+    start: float
+    end: float
+    num_seqs: int
+    num_tokens: int
+    scheduler: SchedulerStats
+    cache: CacheStats
+
+
+@dataclass
+class Completion:
+    """A finished request: its n samples in fork order."""
+
+    request_id: int
+    prompt_token_ids: list[int]
+    token_ids: list[list[int]]
+    texts: list[str] | None
+    finish_reasons: list[str]
+    arrival_time: float
+    first_token_time: float
+    finish_time: float
+
+
+class LLM:
+    def __init__(
+            self,
+            model_path: str,
+            scheduler_config: SchedulerConfig = SchedulerConfig(),
+            cache_config: CacheConfig = CacheConfig(),
+            *,
+            dtype: torch.dtype | str = torch.bfloat16,
+            num_blocks: int | None = None,
+            gpu_memory_utilization: float = 0.9,
+            seed: int | None = None,
+            load_tokenizer: bool | None = None,
+            random_weights_seed: int | None = None,
+            cuda_graphs: bool = True,
+    ) -> None:
+        self.device = require_cuda(cache_config.device)
+        self.dtype = resolve_dtype(dtype)
+        torch.cuda.set_device(self.device)
+        self.model = load_model(model_path, self.dtype, self.device, random_weights_seed=random_weights_seed)
+        spec = self.model.spec
+        if scheduler_config.max_model_len > spec.max_positions:
+            raise ValueError(f"max_model_len = {scheduler_config.max_model_len} exceeds the model's "
+                             f"max_position_embeddings = {spec.max_positions}")
+        self.tokenizer = None
+        if load_tokenizer is None:
+            load_tokenizer = any(os.path.isfile(os.path.join(model_path, f))
+                                 for f in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json"))
+        if load_tokenizer:
+            from transformers import AutoTokenizer          # text <-> ids only; no model code
+            self.tokenizer = AutoTokenizer.from_pretrained(model_path)
+        if scheduler_config.eos_token_id == -1:
+            scheduler_config = replace(scheduler_config, eos_token_id=self._eos_token_id())
+        self.scheduler_config = scheduler_config
+        self.cache_config = cache_config
+        needs_state = any(state for _, state in self.model.cache_needs())
+        state_slots = scheduler_config.max_num_seqs if needs_state else 0
+        if num_blocks is None:
+            num_blocks = self._size_cache(gpu_memory_utilization, state_slots)
+        self.layout, self.cache, self.storage = build_cache(
+            self.model, cache_config.block_size, num_blocks, caching=cache_config.caching, num_state_slots=state_slots)
+        self.scheduler = Scheduler(scheduler_config, self.cache)
+        self.runner = StepRunner(self.model, self.cache, self.storage, cuda_graphs=cuda_graphs,
+                                 max_model_len=scheduler_config.max_model_len,
+                                 max_decode_batch=scheduler_config.max_num_seqs)
+        self.sampler = Sampler(self.model.rt.ops, self.device, seed)
+        self.steps: list[StepRecord] = []
+        logger.info("cache: %d pages of %d tokens", num_blocks, cache_config.block_size)
+
+    # ------------------------------------------------------------------ set-up helpers
+    def _eos_token_id(self) -> int:
+        if self.tokenizer is not None and self.tokenizer.eos_token_id is not None:
+            return int(self.tokenizer.eos_token_id)
+        return self.model.spec.eos_token_id
+
+    def _size_cache(self, utilisation: float, state_slots: int) -> int:
+        """Runs one worst-case step on a throwaway cache, then gives the pool what is left under the limit."""
+        cfg, page = self.scheduler_config, self.cache_config.block_size
+        tokens = min(cfg.max_num_batched_tokens, cfg.max_model_len - 1)
+        if cfg.prefill_chunk:
+            tokens = min(tokens, cfg.prefill_chunk)
+        pages = -(-tokens // page) + 1
+        _, manager, storage = build_cache(self.model, page, pages, caching=False, num_state_slots=max(state_slots, 1))
+        runner = StepRunner(self.model, manager, storage, cuda_graphs=False)
+        torch.cuda.synchronize(self.device)
+        torch.cuda.reset_peak_memory_stats(self.device)
+        baseline = torch.cuda.memory_allocated(self.device)
+        manager.admit(0, [0] * tokens)
+        runner.step([StepEntry(0, [0] * tokens, [tokens - 1])])
+        torch.cuda.synchronize(self.device)
+        peak = torch.cuda.max_memory_allocated(self.device) - baseline
+        del runner, manager, storage
+        torch.cuda.empty_cache()
+        free, total = torch.cuda.mem_get_info(self.device)
+        layout = plan_layout(self.model.cache_needs(), page)
+        per_page = sum(DeviceCacheStorage.bytes_per_page(layout, self.dtype))
+        budget = total * utilisation - (total - free) - peak
+        num_blocks = int(budget // max(per_page, 1))
+        logger.info("warm-up: %d tokens, peak activations %.2f GiB", tokens, peak / 2 ** 30)
+        if num_blocks <= 0:
+            raise RuntimeError("no memory left for the cache; lower max_num_batched_tokens or raise gpu_memory_utilization")
+        return num_blocks
+
+    # ------------------------------------------------------------------ the loop
+    def add_request(self, prompt: str | list[int], params: SamplingParams = SamplingParams(),
+                    arrival_time: float | None = None) -> int:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("a text prompt needs a tokenizer; pass token ids or load_tokenizer=True")
+            token_ids = self.tokenizer.encode(prompt)
+        else:
+            token_ids = [int(t) for t in prompt]
+        vocab = self.model.spec.vocab_size
+        if any(t < 0 or t >= vocab for t in token_ids):
+            raise ValueError(f"prompt holds token ids outside the vocabulary of {vocab}")
+        return self.scheduler.add_request(token_ids, params, time.perf_counter() if arrival_time is None else arrival_time)
+
+    def _run(self, batch: list[ScheduledSeq]) -> list[list[int]]:
+        entries, temperatures, draws, rows = [], [], [], []
+        row = 0
+        for seq, fed, num_samples in batch:
+            entries.append(StepEntry(seq.seq_id, fed, [len(fed) - 1] if num_samples else []))
+            for i in range(num_samples):
+                index = seq.sample_index if num_samples == 1 else i
+                temperatures.append(seq.params.temperature)
+                draws.append((seq.request_id, index, len(seq.output_token_ids)))
+                rows.append(row)
+            row += 1 if num_samples else 0
+        logits = self.runner.step(entries)
+        tokens = self.sampler.sample(logits, temperatures, draws, rows)
+        out, i = [], 0
+        for _, _, num_samples in batch:
+            out.append(tokens[i:i + num_samples])
+            i += num_samples
+        return out
+
+    def step(self) -> list[RequestOutput]:
+        start = time.perf_counter()
+        batch = self.scheduler.schedule(start)
+        if not batch:
+            raise RuntimeError("the scheduler produced an empty step")
+        sampled = self._run(batch)
+        end = time.perf_counter()
+        outputs = self.scheduler.postprocess(batch, sampled, end)
+        self.steps.append(StepRecord(start, end, len(batch), sum(len(fed) for _, fed, _ in batch),
+                                     self.scheduler.stats(), self.cache.stats()))
+        return outputs
+
+    def generate(self, prompts: list[str] | list[list[int]],
+                 params: SamplingParams | list[SamplingParams] = SamplingParams()) -> list[Completion]:
+        """Runs the prompts to completion; results come back in prompt order."""
+        params = params if isinstance(params, list) else [params] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError(f"{len(prompts)} prompts but {len(params)} sampling parameter sets")
+        order = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        done: dict[int, RequestOutput] = {}
+        while self.scheduler.has_unfinished():
+            for output in self.step():
+                done[output.request_id] = output
+        return [self._completion(done[r]) for r in order]
+
+    def _completion(self, output: RequestOutput) -> Completion:
+        seqs = sorted(output.sequences, key=lambda s: s.sample_index)
+        token_ids = [list(s.output_token_ids) for s in seqs]
+        texts = None
+        if self.tokenizer is not None:
+            texts = [self.tokenizer.decode(t, skip_special_tokens=True) for t in token_ids]
+        return Completion(
+            request_id=output.request_id,
+            prompt_token_ids=list(seqs[0].prompt_token_ids),
+            token_ids=token_ids,
+            texts=texts,
+            finish_reasons=[s.finish_reason for s in seqs],
+            arrival_time=seqs[0].arrival_time,
+            first_token_time=min(s.first_token_time for s in seqs),
+            finish_time=max(s.finish_time for s in seqs),
+        )

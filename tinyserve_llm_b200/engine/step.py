@@ -78,8 +78,27 @@ def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
 
+class _DecodeGraph:
+    """A captured decode step for one batch size: static index buffer in, static logits out."""
+
+    def __init__(self, graph: torch.cuda.CUDAGraph, index_buffer: torch.Tensor, logits: torch.Tensor,
+                 widths: list[int]) -> None:
+        self.graph = graph
+        self.index_buffer = index_buffer
+        self.logits = logits
+        self.widths = widths
+
+
 class StepRunner:
-    def __init__(self, model: DecoderModel, manager: CacheManager, storage: DeviceCacheStorage) -> None:
+    """
+    `cuda_graphs`: steps in which every request feeds one token (decoding) are replayed from a CUDA
+    graph captured per batch-size bucket, when every part of the model is graph safe.  The logits
+    such a step returns live in the graph's static buffer and are overwritten by the next decode
+    step of the same bucket: consume them (sample, copy) before stepping again.
+    """
+
+    def __init__(self, model: DecoderModel, manager: CacheManager, storage: DeviceCacheStorage, *,
+                 cuda_graphs: bool = True, max_decode_batch: int = 256, max_model_len: int | None = None) -> None:
         self.model = model
         self.manager = manager
         self.storage = storage
@@ -88,6 +107,13 @@ class StepRunner:
         self._staging: torch.Tensor | None = None       # pinned int32 buffer for the step's index data
         self._staged = torch.cuda.Event()
         self._staged.record()
+        self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
+        self.max_decode_batch = max_decode_batch
+        longest = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
+        self._graph_widths = [max(1, min(pool.num_pages, -(-longest // manager.page_tokens)))
+                              for pool in manager.pools]
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ packing
     def _validate(self, entries: Sequence[StepEntry]) -> None:
@@ -118,7 +144,13 @@ class StepRunner:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.seq_id!r}: wanted place {w} outside its {n} tokens")
 
-    def _pack(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _pack(self, entries: Sequence[StepEntry], pad_to: int | None = None,
+              widths: list[int] | None = None, into: torch.Tensor | None = None) -> StepContext:
+        """
+        Index data of the step in one pinned buffer, one copy to the device.  `pad_to` (decode
+        graphs) pads the batch to a fixed number of single-token requests, padding rows marked by
+        seq_of_token = -1, and asks for the logits of every row; `into` is the static device buffer.
+        """
         mgr = self.manager
         ids: list[int] = []
         positions: list[int] = []
@@ -137,16 +169,29 @@ class StepRunner:
             ctx_lens.append(first + n)
             slots.append(state.state_slot)
             seq_ids.append(e.seq_id)
-        T, S, R = len(ids), len(entries), len(rows)
         groups = len(mgr.pools)
-        widths = [max(1, max(len(mgr.seqs[e.seq_id].tables[g]) for e in entries)) for g in range(groups)]
+        if pad_to is not None:
+            extra = pad_to - len(entries)
+            ids.extend([0] * extra)
+            positions.extend([0] * extra)
+            seq_of_token.extend([-1] * extra)
+            cu_q.extend(range(cu_q[-1] + 1, cu_q[-1] + 1 + extra))
+            ctx_lens.extend([0] * extra)
+            slots.extend([-1] * extra)
+            rows = list(range(pad_to))
+        else:
+            widths = [max(1, max(len(mgr.seqs[e.seq_id].tables[g]) for e in entries)) for g in range(groups)]
+        T, S, R = len(ids), len(ctx_lens), len(rows)
         sections = [ids, positions, seq_of_token, cu_q, ctx_lens, rows, slots]
         for g in range(groups):
             flat: list[int] = []
             for e in entries:
                 t = mgr.seqs[e.seq_id].tables[g]
+                if len(t) > widths[g]:
+                    raise ValueError(f"request {e.seq_id!r} holds {len(t)} pages; the step was built for {widths[g]}")
                 flat.extend(t)
                 flat.extend([-1] * (widths[g] - len(t)))
+            flat.extend([-1] * (widths[g] * (S - len(entries))))
             sections.append(flat)
         offsets, total = [], 0
         for sec in sections:
@@ -160,10 +205,15 @@ class StepRunner:
         for off, sec in zip(offsets, sections):
             if sec:
                 host[off:off + len(sec)] = torch.tensor(sec, dtype=torch.int32)
-        dev = host[:total].to(self.device, non_blocking=True)
+        if into is None:
+            dev = host[:total].to(self.device, non_blocking=True)
+        else:
+            dev = into
+            dev[:total].copy_(host[:total], non_blocking=True)
         self._staged.record()
 
         ctx = StepContext(self, T, S, HostView(seq_ids, cu_q, start, ctx_lens, slots))
+        ctx.index_words = total
         view = lambda i, n: dev[offsets[i]:offsets[i] + n]  # noqa: E731
         ctx.token_ids, ctx.positions, ctx.seq_of_token = view(0, T), view(1, T), view(2, T)
         ctx.cu_q, ctx.ctx_lens, ctx.rows, ctx.state_slots = view(3, S + 1), view(4, S), view(5, R), view(6, S)
@@ -175,8 +225,53 @@ class StepRunner:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """float32 [wanted places, vocab] on the device, in the order of the entries and of their `want`."""
         self._validate(entries)
+        if self.cuda_graphs and len(entries) <= self.max_decode_batch and all(len(e.tokens) == 1 for e in entries):
+            return self._decode_step(entries)
         ctx = self._pack(entries)
         x, residual = self.model.forward(ctx)
         if ctx.rows.numel() == 0:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
         return self.model.logits(x, residual, ctx.rows)
+
+    # ------------------------------------------------------------------ decode steps from a CUDA graph
+    @staticmethod
+    def bucket(n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return b
+
+    def _decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        size = self.bucket(len(entries))
+        captured = self._graphs.get(size)
+        if captured is None:
+            captured = self._capture(entries, size)
+        else:
+            self._pack(entries, pad_to=size, widths=captured.widths, into=captured.index_buffer)
+            captured.graph.replay()
+        self.graph_replays += 1
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        if len(wanted) == len(entries):
+            return captured.logits[:len(entries)]
+        if not wanted:
+            return captured.logits[:0]
+        return captured.logits.index_select(0, torch.tensor(wanted, dtype=torch.int64, device=self.device))
+
+    def _capture(self, entries: Sequence[StepEntry], size: int) -> _DecodeGraph:
+        widths = list(self._graph_widths)
+        probe = self._pack(entries, pad_to=size, widths=widths)
+        index_buffer = torch.empty(probe.index_words, dtype=torch.int32, device=self.device)
+        ctx = self._pack(entries, pad_to=size, widths=widths, into=index_buffer)
+        # once eagerly: libraries create their handles and workspaces outside the capture; the
+        # step's keys and values are written by this run and again, identically, by the replay
+        x, residual = self.model.forward(ctx)
+        self.model.logits(x, residual, ctx.rows)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            x, residual = self.model.forward(ctx)
+            logits = self.model.logits(x, residual, ctx.rows)
+        graph.replay()
+        captured = _DecodeGraph(graph, index_buffer, logits, widths)
+        self._graphs[size] = captured
+        return captured

@@ -19,6 +19,8 @@ from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
 
 @register_part("mixer", "attention")
 class PagedAttention(Mixer):
+    graph_safe = True
+
     @classmethod
     def declare(cls, spec: AttentionSpec) -> dict[str, TensorDecl]:
         q = spec.num_heads * spec.head_dim

@@ -49,6 +49,7 @@ class Part:
     """Common base: declares tensors, is constructed from them."""
 
     role = ""
+    graph_safe = False        # True: forward() launches the same kernels whatever the step holds (CUDA graphs)
 
     @classmethod
     def declare(cls, spec: PartSpec) -> dict[str, TensorDecl]:

@@ -16,6 +16,8 @@ from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
 
 @register_part("feed_forward", "gated_mlp")
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     ACTIVATIONS = ("silu",)
 
     @classmethod

@@ -54,6 +54,9 @@ class DecoderModel:
         else:
             self.lm_head = Linear(tensors[spec.lm_head_name], rt)
         self._check_run_list()
+        # A CUDA graph may replay the model only if no part runs host code that depends on the step.
+        self.graph_safe = all(getattr(part, "graph_safe", False) for block in self.blocks
+                              for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm))
 
     def _check_run_list(self) -> None:
         writers: dict[int, int] = {}

@@ -17,6 +17,8 @@ from tinyserve_llm_b200.parts.base import Norm, Runtime, TensorDecl, register_pa
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     @classmethod
     def declare(cls, spec: RMSNormSpec) -> dict[str, TensorDecl]:
         return {"weight": TensorDecl((spec.size,), init="unit")}

@@ -1,0 +1,54 @@
+"""
+Token sampling: greedy at temperature 0, otherwise a draw from softmax(logits / temperature).
+
+tinyserve-llm draws with the Gumbel-max trick in exponential form from one generator stream for
+the whole batch (engine/sampler.py:13-23).  Here the kernel uses counter-based noise keyed per draw
+by (seed, request, sample index, output position), so a request's tokens do not depend on what
+else is in the batch or on how its prompt was cut into portions.
+"""
+
+from __future__ import annotations
+
+import hashlib
+import struct
+from typing import Sequence
+
+import torch
+
+
+def draw_key(seed: int, request_id: int, sample_index: int, position: int) -> tuple[int, int]:
+    """Two 32-bit words for the kernel's Philox key."""
+    digest = hashlib.blake2b(struct.pack("<qqqq", seed, request_id, sample_index, position), digest_size=8).digest()
+    k0, k1 = struct.unpack("<ii", digest)
+    return k0, k1
+
+
+class Sampler:
+    def __init__(self, ops, device: torch.device, seed: int | None = None) -> None:
+        self.ops = ops
+        self.device = device
+        if seed is None:
+            seed = int.from_bytes(__import__("os").urandom(7), "little")
+        self.seed = int(seed)
+
+    def sample(self, logits: torch.Tensor, temperatures: Sequence[float], draws: Sequence[tuple[int, int, int]],
+               rows: Sequence[int] | None = None) -> list[int]:
+        """
+        One token per draw.  `logits` is float32 [R, vocab]; draw i uses logits row rows[i] (default
+        row i), temperature temperatures[i] and noise keyed by draws[i] = (request id, sample index,
+        output position).  Returns Python ints: the step's one device-to-host read.
+        """
+        count = len(draws)
+        if count == 0:
+            return []
+        if rows is not None and list(rows) != list(range(logits.shape[0])):
+            logits = logits.index_select(0, torch.tensor(list(rows), dtype=torch.int64, device=logits.device))
+        packed = torch.empty((count, 3), dtype=torch.int32)
+        temps = torch.tensor(list(temperatures), dtype=torch.float32)
+        packed[:, 0] = temps.view(torch.int32)
+        keys = [draw_key(self.seed, *d) if t > 0 else (0, 0) for d, t in zip(draws, temperatures)]
+        packed[:, 1:] = torch.tensor(keys, dtype=torch.int32)
+        dev = packed.to(self.device, non_blocking=True)
+        temps_dev = dev[:, 0].contiguous().view(torch.float32)
+        keys_dev = dev[:, 1:].contiguous()
+        return self.ops.sample(logits.contiguous(), temps_dev, keys_dev).tolist()

@@ -12,6 +12,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from dataclasses import dataclass
 
 import torch
@@ -95,7 +96,9 @@ class SafetensorsFile:
         if count == 0:
             return torch.empty(entry.shape, dtype=entry.dtype)
         view = memoryview(self._map)[self._data_start + entry.begin: self._data_start + entry.end]
-        flat = torch.frombuffer(view, dtype=entry.dtype, count=count)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)       # the map is read-only; the data is cloned right away
+            flat = torch.frombuffer(view, dtype=entry.dtype, count=count)
         return flat.reshape(entry.shape).clone()
 
     def close(self) -> None:
