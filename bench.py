@@ -1,0 +1,349 @@
+"""
+Serving benchmark: decode tokens per second of a Llama 3.2 1B sized model with random weights on one
+B200, bfloat16, through the engine's own step function; prefill of 2,048 tokens; decode at batch 1
+and 64; the same decode measured end to end through the Python entry point.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--layers L]
+
+One JSON line goes to standard output.  `value` is decoded tokens per second at batch 8 with contexts
+of the configuration's benchmark length, timed on the device with CUDA events around K decode steps
+(graph replay + sampling kernel), every step reading all weights (2.5 GB, far more than the 126 MB
+L2).  `e2e` is the same through LLM.step(): host token ids in, host token ids out, wall clock.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Llama 3.2 1B
+MODEL = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "vocab_size": 128256,
+    "hidden_size": 2048,
+    "intermediate_size": 8192,
+    "num_hidden_layers": 16,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "head_dim": 64,
+    "hidden_act": "silu",
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "max_position_embeddings": 131072,
+    "tie_word_embeddings": True,
+    "attention_bias": False,
+    "mlp_bias": False,
+    "torch_dtype": "bfloat16",
+}
+FULL_LAYERS = 16
+BATCH = 8
+CONTEXT = 4096            # benchmark context length of the configuration
+POINT_CONTEXT = 2048      # contexts of the batch 1 / 8 / 64 points
+PREFILL_TOKENS = 2048
+PAGE = 256
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                data = json.load(f)
+            flat = {}
+            for k, v in data.items():
+                if isinstance(v, (int, float)):
+                    flat[k] = float(v)
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                return flat, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc) -> None:
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        clocks = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        top = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower() == "active" for r in self.rows)]
+        return {"sm_mhz": int(statistics.median(clocks)) if clocks else None,
+                "sm_max_mhz": max(top) if top else None, "reasons": reasons, "samples": len(clocks)}
+
+
+def weight_bytes(cfg: dict, layers: int) -> int:
+    h, i, hd = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    nh, nkv, v = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["vocab_size"]
+    per_layer = h * (nh + 2 * nkv) * hd + nh * hd * h + 3 * i * h + 2 * h
+    return 2 * (layers * per_layer + v * h + h)          # lm head (= embedding, tied) read once; rows gathered are noise
+
+
+def kv_bytes(cfg: dict, layers: int, batch: int, context: int) -> int:
+    return batch * context * 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg: dict, layers: int, tokens: int) -> float:
+    h, i, hd = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
+    nh, nkv, v = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["vocab_size"]
+    gemm = 2.0 * tokens * (h * (nh + 2 * nkv) * hd + nh * hd * h + 3 * i * h)
+    attention = 2.0 * 2.0 * nh * hd * tokens * (tokens + 1) / 2.0
+    return layers * (gemm + attention) + 2.0 * v * h
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from tinyserve_llm_b200 import LLM, CacheConfig, SamplingParams, SchedulerConfig
+    from tinyserve_llm_b200.engine.step import StepEntry
+
+    layers = args.layers
+    cfg = dict(MODEL, num_hidden_layers=layers)
+    folder = tempfile.mkdtemp(prefix="bench_model_")
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    max_len = CONTEXT + steps + warmup + 64
+    pages = 64 * (-(-max_len // PAGE) + 1) + 8
+    llm = LLM(folder, SchedulerConfig(max_model_len=max_len, max_num_seqs=64, max_num_batched_tokens=8192,
+                                      prefill_chunk=2048, watermark=0.0),
+              CacheConfig(block_size=PAGE, caching=False), dtype="bfloat16", num_blocks=pages, seed=0,
+              random_weights_seed=0)
+    ops, runner, cache = llm.model.rt.ops, llm.runner, llm.cache
+    gen = torch.Generator().manual_seed(0)
+
+    def prompts(batch: int, length: int) -> list[list[int]]:
+        return torch.randint(0, cfg["vocab_size"], (batch, length), generator=gen).tolist()
+
+    def start_decoding(batch: int, context: int, budget: int):
+        """Requests with `context`-token prompts, run through the entry point until every one decodes."""
+        params = SamplingParams(max_tokens=budget, temperature=0.0, ignore_eos=True)
+        for p in prompts(batch, context):
+            llm.add_request(p, params)
+        while any(not s.output_token_ids for s in llm.scheduler.running + llm.scheduler.waiting):
+            llm.step()
+
+    def finish_all():
+        while llm.scheduler.has_unfinished():
+            llm.step()
+
+    def device_decode(batch: int, context: int, k: int, w: int):
+        """K decode steps timed on the device: graph replay + sampling kernel, no host read in between."""
+        start_decoding(batch, context, w + k + 2)
+        seqs = list(llm.scheduler.running)
+        entries = []
+        for s in seqs:                                    # reserve the step's slot as the scheduler would
+            cache.extend(s.seq_id, [s.output_token_ids[-1]])
+            entries.append(StepEntry(s.seq_id, [s.output_token_ids[-1]], [0]))
+        temps = torch.zeros(batch, dtype=torch.float32, device=llm.device)
+        keys = torch.zeros((batch, 2), dtype=torch.int32, device=llm.device)
+        for _ in range(w):
+            ops.sample(runner.step(entries), temps, keys)
+        torch.cuda.synchronize()
+        before = ops.launches
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(k):
+            ops.sample(runner.step(entries), temps, keys)
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / k
+        launches = ops.launches - before
+        for s in seqs:
+            cache.commit(s.seq_id, 1)
+        for s in seqs:                                    # hand the sequences back in a consistent state
+            s.output_token_ids.append(0)
+        finish_all()
+        return ms, launches
+
+    # ---- prefill of 2,048 tokens, whole, device timed
+    def prefill_once(seq_id: int) -> float:
+        tokens = prompts(1, PREFILL_TOKENS)[0]
+        assert cache.admit(("prefill", seq_id), tokens)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        runner.step([StepEntry(("prefill", seq_id), tokens, [PREFILL_TOKENS - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        cache.commit(("prefill", seq_id), PREFILL_TOKENS)
+        cache.release(("prefill", seq_id))
+        return begin.elapsed_time(end)
+
+    for i in range(3):
+        prefill_once(i)
+    prefill_ms = statistics.median(prefill_once(10 + i) for i in range(5))
+
+    peak, peak_kind = peaks()
+    with ClockSampler() as clocks:
+        ms, launches = device_decode(BATCH, CONTEXT, steps, warmup)
+        # ---- end to end through the entry point: host token ids in, host token ids out
+        start_decoding(BATCH, CONTEXT, warmup + steps + 2)
+        for _ in range(warmup):
+            llm.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            llm.step()
+        torch.cuda.synchronize()
+        e2e_seconds = time.perf_counter() - t0
+        finish_all()
+    graph = runner._graphs.get(runner.bucket(BATCH))
+    h2d = (graph.index_buffer.numel() * 4 if graph else 0) + BATCH * 3 * 4
+    points = {}
+    for b in (1, 8, 64):
+        pms, _ = device_decode(b, POINT_CONTEXT, max(10, steps // 2), 3)
+        points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+
+    value = BATCH / ms * 1e3
+    moved = weight_bytes(cfg, layers) + kv_bytes(cfg, layers, BATCH, CONTEXT)
+    achieved = moved / (ms * 1e-3) / 1e9
+    flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
+    record = {
+        "metric": "decode tok/s at batch 8 (Llama 3.2 1B, bf16, one B200)",
+        "value": round(value, 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": round(ms, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.2-1B", "layers": layers, "layers_of_model": FULL_LAYERS, "hidden_size": cfg["hidden_size"],
+            "intermediate_size": cfg["intermediate_size"], "num_attention_heads": cfg["num_attention_heads"],
+            "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "vocab_size": cfg["vocab_size"], "global_batch": BATCH, "seq_len": CONTEXT,
+            "points_context_len": POINT_CONTEXT, "prefill_tokens": PREFILL_TOKENS, "page_tokens": PAGE,
+            "parallelism": "single GPU", "cuda_graphs": bool(graph), "l2": "inputs larger than L2 (weights 2.5 GB per step)",
+            "peaks": peak_kind,
+        },
+        "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4)},
+        "points": points,
+        "e2e": {"value": round(BATCH * steps / e2e_seconds, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": BATCH * 4},
+        "gpu_launches": launches,
+        "clocks": clocks.summary(),
+    }
+    return record
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference from baseline/_ref through its own LLM.generate, same model sizes and batch."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "tinyserve_llm")):
+        return {"impl": "reference", "unavailable": "baseline/_ref holds no install of tinyserve-llm"}
+    sys.path.insert(0, ref)
+    try:
+        import torch
+        from tinyserve_llm.engine.interface import CacheConfig
+        from tinyserve_llm.engine.llm_engine import LLM
+        from tinyserve_llm.scheduler.scheduler import SchedulerConfig
+        from tinyserve_llm.scheduler.sequence import SamplingParams
+
+        from tinyserve_llm_b200.weights import write_random_model
+    except Exception as exc:                                  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"import failed: {type(exc).__name__}: {exc}"[:300]}
+    layers = args.layers
+    cfg = dict(MODEL, num_hidden_layers=layers)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    folder = tempfile.mkdtemp(prefix="bench_ref_model_")
+    try:
+        write_random_model(folder, cfg, 0)
+        max_len = CONTEXT + steps + warmup + 64
+        llm = LLM(folder, SchedulerConfig(max_model_len=max_len, max_num_seqs=BATCH,
+                                          max_num_batched_tokens=BATCH * CONTEXT + BATCH),
+                  CacheConfig(block_size=PAGE, caching=False), dtype=torch.bfloat16,
+                  num_blocks=BATCH * (-(-max_len // PAGE) + 1) + 8, seed=0, load_tokenizer=False)
+        gen = torch.Generator().manual_seed(0)
+        prompts = torch.randint(0, cfg["vocab_size"], (BATCH, CONTEXT), generator=gen).tolist()
+        with ClockSampler() as clocks:
+            llm.generate(prompts, SamplingParams(max_tokens=warmup + steps + 1, temperature=0.0, ignore_eos=True))
+        decode = [r for r in llm.steps if r.num_tokens == BATCH and r.num_seqs == BATCH][-steps:]
+        seconds = sum(r.end - r.start for r in decode)
+        value = BATCH * len(decode) / seconds
+    except Exception as exc:                                  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"the reference did not run here: {type(exc).__name__}: {exc}"[:300]}
+    return {
+        "metric": "decode tok/s at batch 8 (Llama 3.2 1B, bf16, one B200)", "value": round(value, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": len(decode), "warmup": warmup, "ms_per_step": round(seconds / len(decode) * 1e3, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)", "impl": "reference",
+        "config": {"model": "Llama-3.2-1B", "layers": layers, "layers_of_model": FULL_LAYERS, "global_batch": BATCH,
+                   "seq_len": CONTEXT, "page_tokens": PAGE, "parallelism": "single GPU",
+                   "timing": "host clock around each decode step of LLM.generate (each ends in a host read)"},
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": BATCH * 8},
+        "clocks": clocks.summary(),
+    }
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=100)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (run with --gpus 1)")
+        return 2
+    record = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(record), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -82,11 +82,12 @@ class _DecodeGraph:
     """A captured decode step for one batch size: static index buffer in, static logits out."""
 
     def __init__(self, graph: torch.cuda.CUDAGraph, index_buffer: torch.Tensor, logits: torch.Tensor,
-                 widths: list[int]) -> None:
+                 widths: list[int], launches: int) -> None:
         self.graph = graph
         self.index_buffer = index_buffer
         self.logits = logits
         self.widths = widths
+        self.launches = launches       # kernels of the engine's own library inside the graph
 
 
 class StepRunner:
@@ -249,6 +250,7 @@ class StepRunner:
         else:
             self._pack(entries, pad_to=size, widths=captured.widths, into=captured.index_buffer)
             captured.graph.replay()
+            self.model.rt.ops.launches += captured.launches
         self.graph_replays += 1
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         if len(wanted) == len(entries):
@@ -268,10 +270,13 @@ class StepRunner:
         self.model.logits(x, residual, ctx.rows)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        ops = self.model.rt.ops
+        before = ops.launches
         with torch.cuda.graph(graph):
             x, residual = self.model.forward(ctx)
             logits = self.model.logits(x, residual, ctx.rows)
+        launches = ops.launches - before
         graph.replay()
-        captured = _DecodeGraph(graph, index_buffer, logits, widths)
+        captured = _DecodeGraph(graph, index_buffer, logits, widths, launches)
         self._graphs[size] = captured
         return captured

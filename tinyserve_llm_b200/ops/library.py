@@ -39,9 +39,7 @@ class Ops:
             raise KernelError(f"cannot load the CUDA kernel library {self.lib_path}: {exc}") from None
         self.lib.ts_last_error.restype = ctypes.c_char_p
         self.lib.ts_abi_version.restype = c_int
-        for name in dir(self.lib):
-            pass
-        self._fast_attention = hasattr(self.lib, "ts_paged_attention_bf16")
+        self.launches = 0            # kernels of this library launched (or captured into a graph) so far
 
     # ------------------------------------------------------------------ helpers
     def _call(self, name: str, *args) -> None:
@@ -49,6 +47,7 @@ class Ops:
         fn.restype = c_int
         if fn(*args) != 0:
             raise KernelError(self.lib.ts_last_error().decode())
+        self.launches += 1
 
     @staticmethod
     def _check(t: torch.Tensor, name: str, dtype: torch.dtype | tuple | None = None, dims: int | None = None) -> None:
