@@ -32,11 +32,12 @@ def pytest_collection_modifyitems(config, items):
 @pytest.fixture(scope="session")
 def model_folders(tmp_path_factory):
     """Model folders of the tiny configurations, written once per session with the random-weights mode."""
-    from tiny_configs import SEED_A, SEED_B, SEED_C, TINY_A, TINY_B, TINY_C, WEIGHTS
+    from tiny_configs import SEED_A, SEED_B, SEED_C, SEED_D, TINY_A, TINY_B, TINY_C, TINY_D, WEIGHTS
     from tinyserve_llm_b200.weights import write_random_model
 
     out = {}
-    for name, raw, seed in (("a", TINY_A, SEED_A), ("b", TINY_B, SEED_B), ("c", TINY_C, SEED_C)):
+    for name, raw, seed in (("a", TINY_A, SEED_A), ("b", TINY_B, SEED_B), ("c", TINY_C, SEED_C),
+                            ("d", TINY_D, SEED_D)):
         folder = tmp_path_factory.mktemp(f"tiny_{name}")
         write_random_model(str(folder), raw, seed, **WEIGHTS)
         out[name] = str(folder)

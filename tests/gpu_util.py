@@ -23,6 +23,8 @@ def make_ctx(q_lens: list[int], ctx_lens: list[int]):
         seq_of_token += [s] * q
         cu_q.append(cu_q[-1] + q)
     return SimpleNamespace(positions=i32(positions), seq_of_token=i32(seq_of_token), num_tokens=len(positions),
+                           cu_q=i32(cu_q), ctx_lens=i32(ctx_lens), max_q_len=max(q_lens), min_q_len=min(q_lens),
+                           max_ctx_len=max(ctx_lens), scratch={},
                            host=SimpleNamespace(cu_q=cu_q, ctx_lens=list(ctx_lens), start=[c - q for q, c in zip(q_lens, ctx_lens)]))
 
 

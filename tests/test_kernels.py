@@ -167,14 +167,21 @@ def plain_paged_attention(q, keys, values, ctx_lens, q_lens, scale, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("generic", [False, True])
 @pytest.mark.parametrize("nh, nkv, hd, page, window", [
     (4, 2, 16, 4, 0), (6, 2, 32, 32, 0), (5, 1, 48, 64, 0), (8, 8, 64, 16, 0), (3, 1, 80, 8, 0),
-    (12, 4, 128, 256, 0), (2, 1, 256, 32, 0), (6, 3, 32, 8, 5), (4, 1, 64, 16, 40)])
-def test_paged_attention(ops, dtype, nh, nkv, hd, page, window):
+    (12, 4, 128, 256, 0), (2, 1, 256, 32, 0), (6, 3, 32, 8, 5), (4, 1, 64, 16, 40),
+    # sizes the tensor-core kernels take in bfloat16: head 64 or 128, pages of a multiple of 64
+    (8, 2, 64, 64, 0), (32, 8, 64, 256, 0), (6, 2, 128, 64, 0), (5, 5, 64, 128, 0), (16, 1, 128, 128, 0),
+    (4, 1, 64, 64, 40), (8, 2, 128, 128, 300), (6, 3, 64, 64, 1)])
+def test_paged_attention(ops, dtype, generic, nh, nkv, hd, page, window):
     """
     A whole prompt, a portion over a cached prefix, a decode over a long context and a single first
     token in one batch, pages scattered and out of order; one score is made to stand out.
+    `generic` forces the generic kernel where the tensor-core kernels would be chosen.
     """
+    if generic and not (dtype == torch.bfloat16 and hd in (64, 128) and page % 64 == 0):
+        pytest.skip("the generic kernel is what runs for these sizes anyway")
     q_lens = [page + 3, 7, 1, 1]
     ctx_lens = [page + 3, 3 * page + 5, 2 * page + 1, 1]
     ctx = make_ctx(q_lens, ctx_lens)
@@ -196,11 +203,41 @@ def test_paged_attention(ops, dtype, nh, nkv, hd, page, window):
     for s in range(len(ctx_lens)):
         fill_cache(binding, s, keys[s], values[s])
     scale = hd ** -0.5
-    got = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, window).cpu().double().view(T, nh, hd)
+    got = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, window, generic=generic)
+    got = got.cpu().double().view(T, nh, hd)
     q = qkv[:, : nh * hd].view(T, nh, hd).double()
     want = plain_paged_attention(q, keys, values, ctx_lens, q_lens, scale, window)
     assert torch.isfinite(got).all(), "a slot nobody wrote was read"
     torch.testing.assert_close(got, plain.rnd(want, act_of(dtype)), **tol(dtype, 2))
+
+
+@pytest.mark.parametrize("hd, g", [(64, 4), (128, 3)])
+def test_tensor_core_attention_on_long_batches(ops, hd, g):
+    """Decode over many splits (contexts up to 2,300 keys), prompts of several tiles, and a decode-only batch."""
+    nkv, page = 2, 128
+    nh = nkv * g
+    for q_lens, ctx_lens in (([1, 1, 1, 1, 1], [2300, 1, 255, 256, 257]), ([200, 1, 130, 64], [200, 900, 1000, 64])):
+        ctx = make_ctx(q_lens, ctx_lens)
+        tables, at = [], 0
+        for c in ctx_lens:
+            n = -(-c // page)
+            tables.append(list(range(at + n - 1, at - 1, -1)))          # pages in descending order
+            at += n
+        binding = make_binding(at + 1, 1, nkv, page, hd, torch.bfloat16, tables)
+        keys = [rand((c, nkv, hd), torch.bfloat16, 40 + s) for s, c in enumerate(ctx_lens)]
+        values = [rand((c, nkv, hd), torch.bfloat16, 50 + s) for s, c in enumerate(ctx_lens)]
+        for s in range(len(ctx_lens)):
+            fill_cache(binding, s, keys[s], values[s])
+        T = ctx.num_tokens
+        qkv = rand((T, (nh + 2 * nkv) * hd), torch.bfloat16, 12)
+        qkv[0, :hd] = (keys[0][3, 0].float() * 3).to(torch.bfloat16)   # row 0 attends to its key 3 above all
+        scale = hd ** -0.5
+        got = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0).cpu().double().view(T, nh, hd)
+        want = plain_paged_attention(qkv[:, : nh * hd].view(T, nh, hd).double(), keys, values, ctx_lens, q_lens, scale, 0)
+        assert torch.isfinite(got).all()
+        torch.testing.assert_close(got, plain.rnd(want, "bfloat16"), **tol(torch.bfloat16, 2))
+        same = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0, generic=True).cpu().double()
+        torch.testing.assert_close(got.view(T, -1), same, **tol(torch.bfloat16, 2))
 
 
 def test_kernels_refuse_sizes_they_do_not_take(ops):

@@ -12,11 +12,11 @@ import pytest
 import torch
 
 import replay_util as ru
-from tiny_configs import TINY_A, TINY_B, TINY_C
+from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 
-RAW = {"a": TINY_A, "b": TINY_B, "c": TINY_C}
+RAW = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D}
 
 # float32: both sides are exact up to float32 rounding of sums a few hundred terms long.
 # bfloat16: the plain implementation rounds where the engine does, so what is left is the order of
@@ -37,6 +37,8 @@ def requests_for(name):
     single = {"whole": ru.random_ids(vocab, longest, 1), "tail": ru.random_ids(vocab, longest - 33, 2),
               "cut": ru.random_ids(vocab, longest - 7, 3), "short": ru.random_ids(vocab, 3, 4)}
     lengths = [150, 90, 200, 33, 120, 180, 64, 129, 65, 2]
+    if longest > 800:                                   # the model with long positions: several decode splits
+        lengths = [700, 90, 513, 33, 256, 180, 64, 129, 65, 2]
     mixed = {f"m{i}": ru.random_ids(vocab, n, 10 + i) for i, n in enumerate(lengths)}
     return single, mixed
 
@@ -52,7 +54,7 @@ def build_trace(single, mixed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_every_way_of_cutting_gives_the_plain_logits(name, dtype, model_folders, tmp_path):
     single, mixed = requests_for(name)
     trace = build_trace(single, mixed)

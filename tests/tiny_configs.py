@@ -75,7 +75,29 @@ TINY_C = {
 }
 PAGE_C = 64
 
+# Head size 64 and a page size the replay program uses (64): the sizes the bfloat16 tensor-core
+# attention kernels take; three query heads per kv head.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "model_type": "llama",
+    "vocab_size": 640,
+    "hidden_size": 160,
+    "intermediate_size": 336,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 6,
+    "num_key_value_heads": 2,
+    "head_dim": 64,
+    "hidden_act": "silu",
+    "rms_norm_eps": 1e-5,
+    "rope_theta": 50000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 2.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 256},
+    "max_position_embeddings": 1100,
+    "tie_word_embeddings": True,
+}
+PAGE_D = 64
+
 # Seeds and spreads of the random weights the tests and the golden files use.  Norm weights spread
 # widely (1 + N(0, 0.25)) so that a norm weight left out or misplaced changes the logits visibly.
 WEIGHTS = {"std": 0.05, "unit_std": 0.25}
-SEED_A, SEED_B, SEED_C = 11, 22, 33
+SEED_A, SEED_B, SEED_C, SEED_D = 11, 22, 33, 44

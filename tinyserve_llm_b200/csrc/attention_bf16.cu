@@ -1,0 +1,490 @@
+// Paged causal grouped-query attention for bfloat16 on tensor cores (mma.sync m16n8k16, float32
+// accumulation), for head sizes 64 and 128 and pages of a multiple of 64 tokens.  Other sizes go
+// to the generic kernel.  Two kernels share one tile routine:
+//
+//  * prefill: a CTA takes 64 consecutive tokens of one request for one query head and walks the
+//    request's keys in tiles of 64 through a two-stage cp.async pipeline, online softmax in float32.
+//    It serves whole prompts and portions over a cached prefix: a query at position p sees keys
+//    max(0, p - window + 1) .. p (attention/torch_paged.py:36-45 of the reference, by positions).
+//  * decode: requests that feed one token.  The g query heads that share a kv head are the rows of
+//    one tile; the keys are cut into splits of 256 (fixed by key index, so the sums do not depend on
+//    the batch); a CTA takes one split, each of its 4 warps one tile of 64 keys; warps merge in
+//    shared memory and write (max, sum, output) partials to scratch; a second kernel combines the
+//    splits of each head.
+//
+// Keys and values beyond the request's length (the unwritten tail of its last page) are zero-filled
+// on load and masked by select, so whatever those slots hold never reaches a result.
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE = 64;           // keys per tile, queries per prefill CTA
+constexpr int SPLIT = 256;         // keys per decode split
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+    const int bytes = valid ? 16 : 0;                       // 0: the 16 bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A tile in shared memory: ROWS rows of HD bfloat16, 16-byte chunks XOR-swizzled by the row.
+template <int HD>
+__device__ __forceinline__ __nv_bfloat16* tile_at(__nv_bfloat16* tile, int row, int chunk) {
+    return tile + row * HD + ((chunk ^ (row & 7)) << 3);
+}
+
+// Loads `rows` rows of HD bfloat16 (row r from src + r * src_stride) into a swizzled tile with the
+// `nthreads` threads given; rows >= valid_rows are zero-filled.
+template <int HD>
+__device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat16* src, long long src_stride,
+                                          int rows, int valid_rows, int tid, int nthreads) {
+    constexpr int CHUNKS = HD / 8;
+    for (int i = tid; i < rows * CHUNKS; i += nthreads) {
+        const int r = i / CHUNKS, c = i % CHUNKS;
+        const bool ok = r < valid_rows;
+        cp_async16(tile_at<HD>(tile, r, c), src + (ok ? (long long)r * src_stride + c * 8 : 0), ok);
+    }
+}
+
+// Running softmax state of the two rows a thread owns (lane/4 and lane/4 + 8 of the warp's 16).
+template <int HD>
+struct RowState {
+    float m[2] = {-INFINITY, -INFINITY};    // running maximum of score * scale * log2(e)
+    float l[2] = {0.f, 0.f};                // this thread's share of the running sum
+    float o[HD / 8][4];
+    __device__ RowState() {
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
+    }
+};
+
+// One tile of 64 keys against the warp's 16 query rows.  q: the rows' A fragments; k_tile/v_tile:
+// swizzled [64][HD]; key0: index of the tile's first key; pos[2]: positions of the thread's two rows
+// (keys lo[i]..pos[i] are visible).
+template <int HD>
+__device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q)[HD / 16][4], __nv_bfloat16* k_tile,
+                                            __nv_bfloat16* v_tile, int key0, const int (&pos)[2], const int (&lo)[2],
+                                            float scale_log2, int lane) {
+    float s[TILE / 8][4];
+#pragma unroll
+    for (int n = 0; n < TILE / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+    // S = Q K^T
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int nb = 0; nb < TILE / 16; ++nb) {
+            uint32_t b[4];
+            const int row = nb * 16 + (lane & 7) + ((lane >> 4) << 3);
+            const int chunk = kk * 2 + ((lane >> 3) & 1);
+            ldmatrix_x4(b, tile_at<HD>(k_tile, row, chunk));
+            mma_bf16(s[2 * nb], q[kk], b[0], b[1]);
+            mma_bf16(s[2 * nb + 1], q[kk], b[2], b[3]);
+        }
+    }
+    // mask, scale into the log2 domain, running maximum
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < TILE / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int key = key0 + n * 8 + ((lane & 3) << 1) + (e & 1);
+            const bool visible = key <= pos[r] && key >= lo[r];
+            const float v = visible ? s[n][e] * scale_log2 : -INFINITY;
+            s[n][e] = v;
+            tile_max[r] = fmaxf(tile_max[r], v);
+        }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
+        tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
+        const float m_new = fmaxf(st.m[r], tile_max[r]);
+        m_use[r] = m_new == -INFINITY ? 0.f : m_new;          // a row that has seen no key yet
+        corr[r] = exp2f(st.m[r] - m_use[r]);                  // 0 when the old maximum was -inf
+        st.m[r] = m_new;
+        st.l[r] *= corr[r];
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        st.o[n][0] *= corr[0]; st.o[n][1] *= corr[0];
+        st.o[n][2] *= corr[1]; st.o[n][3] *= corr[1];
+    }
+    // P = exp2(S - m), sums in float32, P rounded to bfloat16 for the second product
+    uint32_t p[TILE / 16][4];
+#pragma unroll
+    for (int n = 0; n < TILE / 8; ++n) {
+        const float p0 = exp2f(s[n][0] - m_use[0]), p1 = exp2f(s[n][1] - m_use[0]);
+        const float p2 = exp2f(s[n][2] - m_use[1]), p3 = exp2f(s[n][3] - m_use[1]);
+        st.l[0] += p0 + p1;
+        st.l[1] += p2 + p3;
+        p[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
+        p[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+    // O += P V
+#pragma unroll
+    for (int kk = 0; kk < TILE / 16; ++kk) {
+#pragma unroll
+        for (int nb = 0; nb < HD / 16; ++nb) {
+            uint32_t b[4];
+            const int row = kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            const int chunk = nb * 2 + (lane >> 4);
+            ldmatrix_x4_trans(b, tile_at<HD>(v_tile, row, chunk));
+            mma_bf16(st.o[2 * nb], p[kk], b[0], b[1]);
+            mma_bf16(st.o[2 * nb + 1], p[kk], b[2], b[3]);
+        }
+    }
+}
+
+struct AttnParams {
+    const __nv_bfloat16* qkv;
+    __nv_bfloat16* out;
+    const __nv_bfloat16* k_pool;
+    const __nv_bfloat16* v_pool;
+    KVGeometry geo;
+    const int* block_table;
+    int table_width;
+    const int* cu_q;
+    const int* ctx_lens;
+    int num_seqs, nh, nkv;
+    float scale_log2;
+    int window;
+    // decode only
+    float* partial_o;      // [seq][head][split][HD]
+    float* partial_ml;     // [seq][head][split][2]
+    int max_splits;
+};
+
+// Address of key (or value) row `key` of kv head `kvh` of the request whose table is given; null if
+// the page was given back.
+template <int HD>
+__device__ __forceinline__ const __nv_bfloat16* kv_row(const __nv_bfloat16* pool, const KVGeometry& geo,
+                                                       const int* table, int kvh, int key) {
+    const int page = table[key / geo.page_tokens];
+    if (page < 0 || page >= geo.num_pages) return nullptr;
+    return pool + (long long)page * geo.page_stride + geo.entry_offset + ((long long)kvh * geo.page_tokens + key % geo.page_tokens) * HD;
+}
+
+// ------------------------------------------------------------------------------------------------ prefill
+template <int HD>
+__global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);             // [64][HD]
+    __nv_bfloat16* kv_tiles = q_tile + TILE * HD;                                     // 2 stages x (K, V) x [64][HD]
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
+    if (q_len <= 1) return;                                                           // decode rows go to the other kernel
+    const int tiles = (q_len + TILE - 1) / TILE;
+    const int tile_index = tiles - 1 - (int)blockIdx.x;                               // long tiles first
+    if (tile_index < 0) return;
+    const int ctx = p.ctx_lens[seq];
+    const int row0 = tile_index * TILE;                                               // first query of the tile, within the step
+    const int rows = min(TILE, q_len - row0);
+    const int pos0 = ctx - q_len + row0;                                              // position of that query
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = head / (p.nh / p.nkv);
+    const int row_width = (p.nh + 2 * p.nkv) * HD;
+    const int* table = p.block_table + (long long)seq * p.table_width;
+
+    load_tile<HD>(q_tile, p.qkv + (long long)(q_begin + row0) * row_width + (long long)head * HD, row_width, TILE, rows,
+                  tid, 128);
+    cp_async_commit();
+
+    const int last_pos = pos0 + rows - 1;
+    const int first_key = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int kt_begin = first_key / TILE, kt_end = last_pos / TILE + 1;
+
+    auto issue = [&](int kt, int stage) {
+        __nv_bfloat16* k_tile = kv_tiles + stage * 2 * TILE * HD;
+        __nv_bfloat16* v_tile = k_tile + TILE * HD;
+        const int key0 = kt * TILE;
+        const __nv_bfloat16* k_src = kv_row<HD>(p.k_pool, p.geo, table, kvh, key0);
+        const __nv_bfloat16* v_src = kv_row<HD>(p.v_pool, p.geo, table, kvh, key0);
+        const int valid = k_src ? min(TILE, ctx - key0) : 0;
+        load_tile<HD>(k_tile, k_src ? k_src : p.k_pool, HD, TILE, valid, tid, 128);
+        load_tile<HD>(v_tile, v_src ? v_src : p.v_pool, HD, TILE, valid, tid, 128);
+        cp_async_commit();
+    };
+
+    issue(kt_begin, 0);
+    cp_async_wait<1>();                      // the query tile has landed
+    __syncthreads();
+    uint32_t q[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+        const int row = warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        ldmatrix_x4(q[kk], tile_at<HD>(q_tile, row, kk * 2 + (lane >> 4)));
+    }
+    int pos[2], lo[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int tile_row = warp * 16 + (lane >> 2) + r * 8;
+        pos[r] = tile_row < rows ? pos0 + tile_row : -1;                              // -1: a padding row sees nothing
+        lo[r] = p.window > 0 ? max(0, pos[r] - p.window + 1) : 0;
+    }
+    RowState<HD> st;
+    for (int kt = kt_begin; kt < kt_end; ++kt) {
+        const int stage = (kt - kt_begin) & 1;
+        if (kt + 1 < kt_end) {
+            issue(kt + 1, stage ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        __nv_bfloat16* k_tile = kv_tiles + stage * 2 * TILE * HD;
+        // a warp whose rows all lie before this tile's keys has nothing to add
+        if (kt * TILE <= pos0 + min(rows, warp * 16 + 16) - 1)
+            attend_tile<HD>(st, q, k_tile, k_tile + TILE * HD, kt * TILE, pos, lo, p.scale_log2, lane);
+        __syncthreads();
+    }
+    // rows' sums over the quad, then write
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int tile_row = warp * 16 + (lane >> 2) + r * 8;
+        if (tile_row >= rows) continue;
+        const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
+        __nv_bfloat16* o = p.out + ((long long)(q_begin + row0 + tile_row) * p.nh + head) * HD + ((lane & 3) << 1);
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+            *reinterpret_cast<__nv_bfloat162*>(o + n * 8) =
+                __floats2bfloat162_rn(st.o[n][2 * r] * inv, st.o[n][2 * r + 1] * inv);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ decode
+template <int HD>
+__global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    const int q_begin = p.cu_q[seq];
+    if (p.cu_q[seq + 1] - q_begin != 1) return;
+    const int ctx = p.ctx_lens[seq];
+    const int pos = ctx - 1;
+    const int g = p.nh / p.nkv;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int key_begin = split * SPLIT;
+    const bool active = key_begin <= pos && key_begin + SPLIT > first_key;
+    float* part_o = p.partial_o + (((long long)seq * p.nh + kvh * g) * p.max_splits + split) * HD;
+    float* part_ml = p.partial_ml + (((long long)seq * p.nh + kvh * g) * p.max_splits + split) * 2;
+    if (!active) {
+        if (split < p.max_splits && tid < g) {                 // an empty split: the combine skips it
+            part_ml[(long long)tid * p.max_splits * 2] = -INFINITY;
+            part_ml[(long long)tid * p.max_splits * 2 + 1] = 0.f;
+        }
+        return;
+    }
+    // shared memory: per warp a query tile [16][HD], a key tile and a value tile [64][HD]
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw) + warp * (16 + 2 * TILE) * HD;
+    __nv_bfloat16* k_tile = q_tile + 16 * HD;
+    __nv_bfloat16* v_tile = k_tile + TILE * HD;
+    const int row_width = (p.nh + 2 * p.nkv) * HD;
+    const int* table = p.block_table + (long long)seq * p.table_width;
+    const int key0 = key_begin + warp * TILE;
+    const bool warp_active = key0 <= pos && key0 + TILE > first_key;
+    RowState<HD> st;
+    if (warp_active) {
+        // rows 0..g-1 of the query tile are the g heads of this kv head; the rest are zero
+        load_tile<HD>(q_tile, p.qkv + (long long)q_begin * row_width + (long long)kvh * g * HD, HD, 16, g, lane, 32);
+        const __nv_bfloat16* k_src = kv_row<HD>(p.k_pool, p.geo, table, kvh, key0);
+        const __nv_bfloat16* v_src = kv_row<HD>(p.v_pool, p.geo, table, kvh, key0);
+        const int valid = k_src ? min(TILE, ctx - key0) : 0;
+        load_tile<HD>(k_tile, k_src ? k_src : p.k_pool, HD, TILE, valid, lane, 32);
+        cp_async_commit();
+        load_tile<HD>(v_tile, v_src ? v_src : p.v_pool, HD, TILE, valid, lane, 32);
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncwarp();
+        uint32_t q[HD / 16][4];
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            const int row = (lane & 7) + (((lane >> 3) & 1) << 3);
+            ldmatrix_x4(q[kk], tile_at<HD>(q_tile, row, kk * 2 + (lane >> 4)));
+        }
+        const int posv[2] = {pos, pos};
+        const int lov[2] = {first_key, first_key};
+        attend_tile<HD>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+            st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+        }
+    }
+    __syncthreads();                                           // tiles are done with: reuse the memory for the merge
+    float* merge_o = reinterpret_cast<float*>(smem_raw);       // [4 warps][16 rows][HD]
+    float* merge_ml = merge_o + 4 * 16 * HD;                   // [4 warps][16 rows][2]
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + r * 8;
+        float* o = merge_o + ((warp * 16 + row) * HD) + ((lane & 3) << 1);
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            o[n * 8] = st.o[n][2 * r];
+            o[n * 8 + 1] = st.o[n][2 * r + 1];
+        }
+        if ((lane & 3) == 0) {
+            merge_ml[(warp * 16 + row) * 2] = st.m[r];
+            merge_ml[(warp * 16 + row) * 2 + 1] = st.l[r];
+        }
+    }
+    __syncthreads();
+    // rows 0..g-1: merge the four warps in order, one thread per (row, dim)
+    for (int i = tid; i < g * HD; i += 128) {
+        const int row = i / HD, d = i % HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * 16 + row) * 2]);
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = merge_ml[(w * 16 + row) * 2];
+            const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
+            l += merge_ml[(w * 16 + row) * 2 + 1] * f;
+            o += merge_o[(w * 16 + row) * HD + d] * f;
+        }
+        part_o[(long long)row * p.max_splits * HD + d] = o;
+        if (d == 0) {
+            part_ml[(long long)row * p.max_splits * 2] = m;
+            part_ml[(long long)row * p.max_splits * 2 + 1] = l;
+        }
+    }
+}
+
+// One block per (request, head): merges the splits in order and writes the output row.
+template <int HD>
+__global__ void decode_combine_kernel(AttnParams p) {
+    const int seq = blockIdx.y, head = blockIdx.x;
+    const int q_begin = p.cu_q[seq];
+    if (p.cu_q[seq + 1] - q_begin != 1) return;
+    const int ctx = p.ctx_lens[seq];
+    const int splits = (ctx + SPLIT - 1) / SPLIT;
+    const float* part_o = p.partial_o + ((long long)seq * p.nh + head) * p.max_splits * HD;
+    const float* part_ml = p.partial_ml + ((long long)seq * p.nh + head) * p.max_splits * 2;
+    float m = -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[2 * s]);
+    const int d = threadIdx.x;
+    float l = 0.f, o = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = part_ml[2 * s];
+        if (ms == -INFINITY) continue;
+        const float f = exp2f(ms - m);
+        l += part_ml[2 * s + 1] * f;
+        o += part_o[(long long)s * HD + d] * f;
+    }
+    p.out[((long long)q_begin * p.nh + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+}
+
+template <int HD>
+int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, cudaStream_t stream) {
+    if (max_q_len > 1) {
+        const size_t smem = (size_t)(TILE * HD + 4 * TILE * HD) * sizeof(__nv_bfloat16);
+        auto kernel = prefill_attention_kernel<HD>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        dim3 grid((max_q_len + TILE - 1) / TILE, p.nh, p.num_seqs);
+        kernel<<<grid, 128, smem, stream>>>(p);
+        TS_LAUNCH_CHECK("prefill_attention");
+    }
+    if (min_q_len <= 1) {
+        const size_t tiles = (size_t)4 * (16 + 2 * TILE) * HD * sizeof(__nv_bfloat16);
+        const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+        const size_t smem = tiles > merge ? tiles : merge;
+        auto kernel = decode_attention_kernel<HD>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        const int splits = (max_ctx_len + SPLIT - 1) / SPLIT;
+        if (splits > p.max_splits) return ts_fail("decode_attention: %d splits needed, scratch holds %d", splits, p.max_splits);
+        dim3 grid(splits, p.nkv, p.num_seqs);
+        kernel<<<grid, 128, smem, stream>>>(p);
+        TS_LAUNCH_CHECK("decode_attention");
+        decode_combine_kernel<HD><<<dim3(p.nh, p.num_seqs), HD, 0, stream>>>(p);
+        TS_LAUNCH_CHECK("decode_combine");
+    }
+    return 0;
+}
+
+}  // namespace
+
+// Scratch the decode path needs: floats for partial outputs and for (max, sum) pairs.
+TS_API long long ts_attention_bf16_scratch_floats(int num_seqs, int nh, int hd, int max_ctx_len) {
+    const long long splits = (max_ctx_len + SPLIT - 1) / SPLIT;
+    return (long long)num_seqs * nh * splits * (hd + 2);
+}
+
+TS_API int ts_attention_bf16_supported(int hd, int page_tokens, int nh, int nkv) {
+    return (hd == 64 || hd == 128) && page_tokens % TILE == 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16;
+}
+
+// max_q_len / min_q_len: longest and shortest number of tokens a request feeds in this step (which
+// kernels run); max_ctx_len: an upper bound of the requests' lengths (the decode grid and scratch).
+TS_API int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_pool, const void* v_pool,
+                                   long long page_stride, long long entry_offset, int page_tokens, int num_pages,
+                                   const int* block_table, int table_width, const int* cu_q, const int* ctx_lens,
+                                   int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv, int hd,
+                                   float scale, int window, float* scratch, long long scratch_floats,
+                                   cudaStream_t stream) {
+    TS_REQUIRE(ts_attention_bf16_supported(hd, page_tokens, nh, nkv),
+               "paged_attention_bf16: head_dim %d / page %d / heads %d:%d is not taken by the tensor-core kernels", hd,
+               page_tokens, nh, nkv);
+    TS_REQUIRE(num_seqs >= 0 && max_q_len >= min_q_len && window >= 0, "paged_attention_bf16: bad sizes");
+    TS_REQUIRE(num_seqs <= 65535 && nh <= 65535, "paged_attention_bf16: more than 65535 requests or heads in a step");
+    if (num_seqs == 0 || max_q_len <= 0) return 0;
+    AttnParams p;
+    p.qkv = (const __nv_bfloat16*)qkv;
+    p.out = (__nv_bfloat16*)out;
+    p.k_pool = (const __nv_bfloat16*)k_pool;
+    p.v_pool = (const __nv_bfloat16*)v_pool;
+    p.geo = KVGeometry{page_stride, entry_offset, page_tokens, num_pages};
+    p.block_table = block_table;
+    p.table_width = table_width;
+    p.cu_q = cu_q;
+    p.ctx_lens = ctx_lens;
+    p.num_seqs = num_seqs;
+    p.nh = nh;
+    p.nkv = nkv;
+    p.scale_log2 = scale * LOG2E;
+    p.window = window;
+    p.max_splits = (max_ctx_len + SPLIT - 1) / SPLIT;
+    p.partial_o = scratch;
+    p.partial_ml = scratch ? scratch + (long long)num_seqs * nh * p.max_splits * hd : nullptr;
+    if (min_q_len <= 1) {
+        TS_REQUIRE(scratch != nullptr && scratch_floats >= ts_attention_bf16_scratch_floats(num_seqs, nh, hd, max_ctx_len),
+                   "paged_attention_bf16: scratch of %lld floats is too small", scratch_floats);
+        TS_REQUIRE((long long)table_width * page_tokens >= max_ctx_len,
+                   "paged_attention_bf16: block tables of %d pages do not reach %d tokens", table_width, max_ctx_len);
+    }
+    if (hd == 64) return launch<64>(p, max_q_len, min_q_len, max_ctx_len, stream);
+    return launch<128>(p, max_q_len, min_q_len, max_ctx_len, stream);
+}

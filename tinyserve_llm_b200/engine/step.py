@@ -61,8 +61,11 @@ class StepContext:
         self.state_slots: torch.Tensor = None     # int32 [S]
         self.rows: torch.Tensor = None            # int32 [R] flat rows whose logits are wanted
         self.tables: list[torch.Tensor] = []      # per group int32 [S, width]
-        self.max_q_len = max((b - a for a, b in zip(host.cu_q, host.cu_q[1:])), default=0)
-        self.max_ctx_len = max(host.ctx_lens, default=0)
+        lens = [b - a for a, b in zip(host.cu_q, host.cu_q[1:])]
+        self.max_q_len = max(lens, default=0)     # which attention kernels a step needs is decided on the host
+        self.min_q_len = min(lens, default=0)
+        self.max_ctx_len = max(host.ctx_lens, default=0)   # an upper bound; a decode graph sets its bucket's bound
+        self.scratch: dict = {}                   # per-step scratch buffers parts share (keyed by purpose and size)
 
     def binding(self, entry: RunEntry) -> EntryBinding | None:
         base = self._runner.bindings[entry.cache_entry]
@@ -215,6 +218,8 @@ class StepRunner:
 
         ctx = StepContext(self, T, S, HostView(seq_ids, cu_q, start, ctx_lens, slots))
         ctx.index_words = total
+        if pad_to is not None:                    # a graph is replayed for any lengths its tables can hold
+            ctx.max_ctx_len = max(w * mgr.page_tokens for w in widths) if widths else 0
         view = lambda i, n: dev[offsets[i]:offsets[i] + n]  # noqa: E731
         ctx.token_ids, ctx.positions, ctx.seq_of_token = view(0, T), view(1, T), view(2, T)
         ctx.cu_q, ctx.ctx_lens, ctx.rows, ctx.state_slots = view(3, S + 1), view(4, S), view(5, R), view(6, S)

@@ -121,9 +121,35 @@ class Ops:
                    c_int(hd), c_int(1 if binding.writes else 0), c_int(_DTYPE_CODE[qkv.dtype]), _stream())
 
     def paged_attention(self, qkv: torch.Tensor, ctx, binding, nh: int, nkv: int, hd: int, scale: float,
-                        window: int) -> torch.Tensor:
+                        window: int, generic: bool = False) -> torch.Tensor:
+        """
+        [T, nh * hd].  bfloat16 with head size 64 or 128 and pages of a multiple of 64 tokens runs on
+        the tensor-core kernels (prefill tiles and split-key decode); everything else, and
+        `generic=True`, on the generic kernel.
+        """
         self._check(qkv, "qkv", tuple(_DTYPE_CODE), 2)
         out = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
+        if (not generic and qkv.dtype == torch.bfloat16 and getattr(ctx, "cu_q", None) is not None
+                and self.lib.ts_attention_bf16_supported(c_int(hd), c_int(binding.page_tokens), c_int(nh), c_int(nkv))):
+            num_seqs = ctx.ctx_lens.shape[0]
+            scratch, floats = None, 0
+            if ctx.min_q_len <= 1:
+                self.lib.ts_attention_bf16_scratch_floats.restype = c_longlong
+                floats = self.lib.ts_attention_bf16_scratch_floats(c_int(num_seqs), c_int(nh), c_int(hd),
+                                                                   c_int(ctx.max_ctx_len))
+                key = ("attention", floats)
+                scratch = ctx.scratch.get(key)
+                if scratch is None:
+                    scratch = ctx.scratch[key] = torch.empty((floats,), dtype=torch.float32, device=qkv.device)
+            self._call("ts_paged_attention_bf16", _ptr(qkv), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
+                       c_longlong(binding.page_stride), c_longlong(binding.entry_offset), c_int(binding.page_tokens),
+                       c_int(binding.num_pages), _ptr(binding.block_table), c_int(binding.table_width),
+                       _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), c_int(num_seqs), c_int(ctx.max_q_len),
+                       c_int(ctx.min_q_len), c_int(ctx.max_ctx_len), c_int(nh), c_int(nkv), c_int(hd), c_float(scale),
+                       c_int(window), _ptr(scratch), c_longlong(floats), _stream())
+            if ctx.min_q_len <= 1:
+                self.launches += 1 if ctx.max_q_len <= 1 else 2      # decode + combine (+ prefill) in one call
+            return out
         self._call("ts_paged_attention_generic", _ptr(qkv), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
                    c_longlong(binding.page_stride), c_longlong(binding.entry_offset), c_int(binding.page_tokens),
                    c_int(binding.num_pages), _ptr(binding.block_table), c_int(binding.table_width),
