@@ -299,3 +299,30 @@ def test_copy_page_slots(ops, dtype):
     assert torch.equal(k[1, :, :, 5:], k0[1, :, :, 5:]) and torch.equal(v[1, :, :, 5:], v0[1, :, :, 5:])
     keep = [0, 2, 3, 4, 5]
     assert torch.equal(k[keep], k0[keep]) and torch.equal(v[keep], v0[keep])
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("n, k", [(48, 64), (1000, 192), (250, 512), (3072, 2048), (2048, 8192), (16, 32)])
+def test_skinny_bfloat16_product(ops, m, n, k):
+    """The weight-streaming kernel for a few rows of x: any N (also no multiple of 16), K a multiple of 32."""
+    x, w = rand((m, k), torch.bfloat16, 5), rand((n, k), torch.bfloat16, 6, 0.05)
+    want = x.double() @ w.double().T
+    scale = want.abs().max().item()
+    got = ops.linear(x.to(DEV), w.to(DEV)).cpu().double()
+    torch.testing.assert_close(got, plain.rnd(want, "bfloat16"), atol=scale * 2 ** -8, rtol=2 ** -7)
+    wide = ops.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32).cpu().double()
+    torch.testing.assert_close(wide, want, atol=scale * 1e-5, rtol=1e-4)
+    # a row's result does not depend on the rows beside it
+    alone = ops.linear(x[:1].contiguous().to(DEV), w.to(DEV), out_dtype=torch.float32).cpu()
+    assert torch.equal(alone[0], ops.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32).cpu()[0])
+
+
+@pytest.mark.parametrize("m", [1, 8, 20, 40])
+@pytest.mark.parametrize("inter, k", [(176, 64), (500, 192), (8192, 2048), (5, 32)])
+def test_linear_with_swiglu_epilogue(ops, m, inter, k):
+    x, w = rand((m, k), torch.bfloat16, 7), rand((2 * inter, k), torch.bfloat16, 8, 0.2)
+    gate_up = plain.rnd(x.double() @ w.double().T, "bfloat16")
+    want = plain.swiglu(gate_up, "bfloat16")
+    got = ops.linear_swiglu(x.to(DEV), w.to(DEV)).cpu().double()
+    scale = want.abs().max().item()
+    torch.testing.assert_close(got, want, atol=scale * 2 ** -7, rtol=2 ** -6)

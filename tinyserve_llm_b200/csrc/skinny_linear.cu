@@ -1,0 +1,195 @@
+// y = x . W^T for a handful of rows of x (decode steps): bfloat16 inputs, float32 accumulation on
+// tensor cores (mma.sync m16n8k16), output bfloat16 or float32.  The weight is the tall operand:
+// a CTA takes 16 rows of W, its warps split K between them in blocks of 32, every thread streams W
+// with 16-byte loads straight from global memory (each warp instruction reads 8 rows x 64 contiguous
+// bytes), partial sums meet in shared memory in warp order.  The k indices inside a block of 32 are
+// permuted the same way for both operands, so a thread's 8 contiguous weights and 8 contiguous
+// activations feed two mma instructions without any shuffle.
+//
+// Epilogues: plain store, or SwiGLU: the CTA's 16 rows are 8 gate rows and the 8 up rows that belong
+// to them, and it stores round(silu(gate)) * up (model/llama.py:80-83 of the reference).
+//
+// The split of K depends on N and K only, never on the number of rows of x, so a row's result does
+// not depend on what else is in the batch.
+#include "common.cuh"
+
+namespace {
+
+enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {          // weights are read once: do not keep them in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+template <typename OUT>
+__device__ __forceinline__ void store_out(OUT* p, float v);
+template <>
+__device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// MT: tiles of 8 rows of x; WARPS: warps per CTA (the split of K); UNROLL: k-blocks in flight per warp.
+template <int MT, int WARPS, int EPI, typename OUT>
+__global__ void __launch_bounds__(WARPS * 32)
+skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x, OUT* __restrict__ y,
+                     int M, int N, int K, long long ldx, long long ldy, int inter) {
+    constexpr int UNROLL = 4;
+    __shared__ float partial[WARPS][MT][32][4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, c = lane & 3;
+    // the two rows of W this thread streams (fragment rows r and r + 8)
+    long long row_lo, row_hi;
+    int rows_valid;                                   // output rows this CTA really has (<= 16, or <= 8 pairs)
+    if (EPI == EPI_SWIGLU) {
+        const int base = blockIdx.x * 8;
+        rows_valid = min(8, inter - base);
+        row_lo = base + min(r, rows_valid - 1);
+        row_hi = (long long)inter + base + min(r, rows_valid - 1);
+    } else {
+        const int base = blockIdx.x * 16;
+        rows_valid = min(16, N - base);
+        row_lo = base + min(r, rows_valid - 1);
+        row_hi = base + min(r + 8, rows_valid - 1);
+    }
+    const __nv_bfloat16* w_lo = W + row_lo * K + c * 8;
+    const __nv_bfloat16* w_hi = W + row_hi * K + c * 8;
+    const __nv_bfloat16* x_row[MT];
+    bool x_ok[MT];
+#pragma unroll
+    for (int t = 0; t < MT; ++t) {
+        const int token = t * 8 + r;
+        x_ok[t] = token < M;
+        x_row[t] = x + (long long)(x_ok[t] ? token : 0) * ldx + c * 8;
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+
+    const int kblocks = K / 32;
+    for (int kb0 = warp * UNROLL; kb0 < kblocks; kb0 += WARPS * UNROLL) {
+        uint4 wl[UNROLL], wh[UNROLL], xv[UNROLL][MT];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int kb = kb0 + u;
+            if (kb < kblocks) {
+                wl[u] = ld_stream(w_lo + kb * 32);
+                wh[u] = ld_stream(w_hi + kb * 32);
+#pragma unroll
+                for (int t = 0; t < MT; ++t)
+                    xv[u][t] = x_ok[t] ? *reinterpret_cast<const uint4*>(x_row[t] + kb * 32) : make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (kb0 + u < kblocks) {
+#pragma unroll
+                for (int t = 0; t < MT; ++t) {
+                    mma_bf16(acc[t], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv[u][t].x, xv[u][t].y);
+                    mma_bf16(acc[t], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv[u][t].z, xv[u][t].w);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < MT; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) partial[warp][t][lane][e] = acc[t][e];
+    __syncthreads();
+    // the warps' partial sums in warp order; thread (t, lane, e) owns row lane/4 (+8 for e >= 2), token t*8 + (lane%4)*2 + e%2
+    if (EPI == EPI_SWIGLU) {
+        for (int i = threadIdx.x; i < MT * 32 * 2; i += WARPS * 32) {
+            const int t = i / 64, l = (i / 2) % 32, e = i % 2;
+            float gate = 0.f, up = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                gate += partial[w][t][l][e];
+                up += partial[w][t][l][e + 2];
+            }
+            const int row = l >> 2, token = t * 8 + ((l & 3) << 1) + e;
+            if (row < rows_valid && token < M) {
+                // gate and up are materialised in bfloat16 by the reference before the activation
+                const float g = round_to<__nv_bfloat16>(gate), u = round_to<__nv_bfloat16>(up);
+                const float silu = round_to<__nv_bfloat16>(g / (1.f + expf(-g)));
+                store_out<OUT>(y + (long long)token * ldy + blockIdx.x * 8 + row, silu * u);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < MT * 32 * 4; i += WARPS * 32) {
+            const int t = i / 128, l = (i / 4) % 32, e = i % 4;
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) v += partial[w][t][l][e];
+            const int row = (l >> 2) + ((e >> 1) << 3), token = t * 8 + ((l & 3) << 1) + (e & 1);
+            if (row < rows_valid && token < M) store_out<OUT>(y + (long long)token * ldy + blockIdx.x * 16 + row, v);
+        }
+    }
+}
+
+template <int MT, int WARPS, int EPI, typename OUT>
+int launch(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
+           cudaStream_t stream) {
+    const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
+    skinny_linear_kernel<MT, WARPS, EPI, OUT><<<tiles, WARPS * 32, 0, stream>>>(
+        (const __nv_bfloat16*)W, (const __nv_bfloat16*)x, (OUT*)y, M, N, K, ldx, ldy, inter);
+    TS_LAUNCH_CHECK("skinny_linear");
+    return 0;
+}
+
+template <int WARPS, int EPI, typename OUT>
+int dispatch_m(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
+               cudaStream_t stream) {
+    if (M <= 8) return launch<1, WARPS, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (M <= 16) return launch<2, WARPS, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    return launch<4, WARPS, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+}
+
+template <int EPI, typename OUT>
+int dispatch_warps(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
+                   cudaStream_t stream) {
+    // enough warps in the grid to keep every SM's memory pipes full: 148 SMs x 16 warps
+    const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
+    const int kblocks = K / 32;
+    int warps = 4;
+    while (warps < 16 && tiles * warps < 148 * 16 && kblocks / (warps * 2) >= 4) warps *= 2;
+    if (warps == 4) return dispatch_m<4, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (warps == 8) return dispatch_m<8, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    return dispatch_m<16, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+}
+
+}  // namespace
+
+TS_API int ts_skinny_linear_max_rows() { return 32; }
+
+// y[M, N] = x[M, K] . W[N, K]^T (epilogue 0), or y[M, N/2] = swiglu of it with W = [gate rows | up rows]
+// (epilogue 1).  out_dtype: TS_BF16 or TS_F32.
+TS_API int ts_skinny_linear(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy,
+                            int epilogue, int out_dtype, cudaStream_t stream) {
+    TS_REQUIRE(M >= 0 && N > 0 && K > 0, "skinny_linear: bad sizes M=%d N=%d K=%d", M, N, K);
+    TS_REQUIRE(M <= ts_skinny_linear_max_rows(), "skinny_linear: %d rows of x; the kernel takes up to %d", M,
+               ts_skinny_linear_max_rows());
+    TS_REQUIRE(K % 32 == 0, "skinny_linear: K=%d is not a multiple of 32", K);
+    TS_REQUIRE(ldx % 8 == 0, "skinny_linear: rows of x must start 16-byte aligned (stride %lld)", ldx);
+    TS_REQUIRE(((uintptr_t)W % 16 == 0) && ((uintptr_t)x % 16 == 0), "skinny_linear: operands must be 16-byte aligned");
+    if (M == 0) return 0;
+    if (epilogue == EPI_SWIGLU) {
+        TS_REQUIRE(N % 2 == 0, "skinny_linear: the SwiGLU epilogue needs gate and up halves (N=%d)", N);
+        TS_REQUIRE(out_dtype == TS_BF16, "skinny_linear: the SwiGLU epilogue stores bfloat16");
+        return dispatch_warps<EPI_SWIGLU, __nv_bfloat16>(W, x, y, M, N, K, ldx, ldy, N / 2, stream);
+    }
+    TS_REQUIRE(epilogue == EPI_STORE, "skinny_linear: unknown epilogue %d", epilogue);
+    if (out_dtype == TS_BF16) return dispatch_warps<EPI_STORE, __nv_bfloat16>(W, x, y, M, N, K, ldx, ldy, 0, stream);
+    if (out_dtype == TS_F32) return dispatch_warps<EPI_STORE, float>(W, x, y, M, N, K, ldx, ldy, 0, stream);
+    return ts_fail("skinny_linear: unknown output dtype code %d", out_dtype);
+}

@@ -40,6 +40,7 @@ class Ops:
         self.lib.ts_last_error.restype = ctypes.c_char_p
         self.lib.ts_abi_version.restype = c_int
         self.launches = 0            # kernels of this library launched (or captured into a graph) so far
+        self.skinny_max_rows = int(self.lib.ts_skinny_linear_max_rows())
 
     # ------------------------------------------------------------------ helpers
     def _call(self, name: str, *args) -> None:
@@ -179,9 +180,36 @@ class Ops:
                        c_int(x.shape[1]), c_longlong(x.shape[1]), c_longlong(weight.shape[1]),
                        c_longlong(weight.shape[0]), _stream())
             return out
-        if out_dtype is not None and out_dtype != x.dtype:
+        out_dtype = out_dtype or x.dtype
+        if self._skinny(x, weight):
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
+            self._call("ts_skinny_linear", _ptr(weight), _ptr(x), _ptr(out), c_int(x.shape[0]), c_int(weight.shape[0]),
+                       c_int(x.shape[1]), c_longlong(x.shape[1]), c_longlong(weight.shape[0]), c_int(0),
+                       c_int(_DTYPE_CODE[out_dtype]), _stream())
+            return out
+        if out_dtype != x.dtype:
             return torch.mm(x, weight.t(), out_dtype=out_dtype)
         return torch.mm(x, weight.t())
+
+    def _skinny(self, x: torch.Tensor, weight: torch.Tensor) -> bool:
+        """A few rows of bfloat16 x (a decode step): the engine's own weight-streaming kernel takes them."""
+        return (x.dtype == torch.bfloat16 and 0 < x.shape[0] <= self.skinny_max_rows and x.shape[1] % 32 == 0
+                and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+    def linear_swiglu(self, x: torch.Tensor, gate_up_weight: torch.Tensor) -> torch.Tensor:
+        """silu(x . Wgate^T) * (x . Wup^T) with Wgate, Wup the two halves of the weight's rows: [M, I]."""
+        self._check(x, "x", tuple(_DTYPE_CODE), 2)
+        self._check(gate_up_weight, "weight", x.dtype, 2)
+        if gate_up_weight.shape[0] % 2 or x.shape[1] != gate_up_weight.shape[1]:
+            raise KernelError("linear_swiglu: the weight must hold gate and up halves over x's columns")
+        if not self._skinny(x, gate_up_weight):
+            return self.silu_mul(self.linear(x, gate_up_weight))
+        inter = gate_up_weight.shape[0] // 2
+        out = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
+        self._call("ts_skinny_linear", _ptr(gate_up_weight), _ptr(x), _ptr(out), c_int(x.shape[0]),
+                   c_int(gate_up_weight.shape[0]), c_int(x.shape[1]), c_longlong(x.shape[1]), c_longlong(inter),
+                   c_int(1), c_int(_DTYPE_CODE[x.dtype]), _stream())
+        return out
 
     def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, keys: torch.Tensor) -> torch.Tensor:
         """int32 [rows]: greedy where temperature is 0, else a draw keyed by keys[row] (two uint32 as int32)."""

@@ -36,4 +36,4 @@ class GatedMLP(FeedForward):
         self.down = Linear(tensors["down_proj.weight"], rt)
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
-        return self.down(self.rt.ops.silu_mul(self.gate_up(x)))
+        return self.down(self.rt.ops.linear_swiglu(x, self.gate_up.weight))
