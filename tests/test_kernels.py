@@ -113,7 +113,7 @@ def test_bfloat16_matrix_product(ops, m, n, k):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh, nkv, hd, rot, page", [(4, 2, 16, 16, 4), (6, 2, 32, 32, 32), (5, 1, 48, 48, 64),
-                                                     (3, 3, 64, 32, 16), (8, 2, 128, 128, 256)])
+                                                     (3, 3, 64, 32, 16), (8, 2, 128, 128, 256), (2, 1, 48, 24, 8)])
 def test_rope_store(ops, dtype, nh, nkv, hd, rot, page):
     """q is rotated in place; k rotated and v raw land in the slots the block table names, nowhere else."""
     act = act_of(dtype)

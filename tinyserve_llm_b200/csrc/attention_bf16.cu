@@ -45,6 +45,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x for x <= 0 (and -inf): one instruction; results below the normal range flush to zero.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -86,7 +92,7 @@ struct RowState {
 // One tile of 64 keys against the warp's 16 query rows.  q: the rows' A fragments; k_tile/v_tile:
 // swizzled [64][HD]; key0: index of the tile's first key; pos[2]: positions of the thread's two rows
 // (keys lo[i]..pos[i] are visible).
-template <int HD>
+template <int HD, bool MASK>
 __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q)[HD / 16][4], __nv_bfloat16* k_tile,
                                             __nv_bfloat16* v_tile, int key0, const int (&pos)[2], const int (&lo)[2],
                                             float scale_log2, int lane) {
@@ -108,18 +114,18 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
             mma_bf16(s[2 * nb + 1], q[kk], b[2], b[3]);
         }
     }
-    // mask, scale into the log2 domain, running maximum
+    // mask, running maximum (of raw scores; the scale is positive and joins the exponent below)
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < TILE / 8; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
-            const int key = key0 + n * 8 + ((lane & 3) << 1) + (e & 1);
-            const bool visible = key <= pos[r] && key >= lo[r];
-            const float v = visible ? s[n][e] * scale_log2 : -INFINITY;
-            s[n][e] = v;
-            tile_max[r] = fmaxf(tile_max[r], v);
+            if (MASK) {                                   // tiles wholly inside every row's range skip the test
+                const int key = key0 + n * 8 + ((lane & 3) << 1) + (e & 1);
+                if (!(key <= pos[r] && key >= lo[r])) s[n][e] = -INFINITY;
+            }
+            tile_max[r] = fmaxf(tile_max[r], s[n][e]);
         }
     }
     float corr[2], m_use[2];
@@ -127,9 +133,9 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
     for (int r = 0; r < 2; ++r) {
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
-        const float m_new = fmaxf(st.m[r], tile_max[r]);
+        const float m_new = fmaxf(st.m[r], tile_max[r] * scale_log2);   // -inf stays -inf
         m_use[r] = m_new == -INFINITY ? 0.f : m_new;          // a row that has seen no key yet
-        corr[r] = exp2f(st.m[r] - m_use[r]);                  // 0 when the old maximum was -inf
+        corr[r] = fast_exp2(st.m[r] - m_use[r]);              // 0 when the old maximum was -inf
         st.m[r] = m_new;
         st.l[r] *= corr[r];
     }
@@ -142,8 +148,8 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
     uint32_t p[TILE / 16][4];
 #pragma unroll
     for (int n = 0; n < TILE / 8; ++n) {
-        const float p0 = exp2f(s[n][0] - m_use[0]), p1 = exp2f(s[n][1] - m_use[0]);
-        const float p2 = exp2f(s[n][2] - m_use[1]), p3 = exp2f(s[n][3] - m_use[1]);
+        const float p0 = fast_exp2(fmaf(s[n][0], scale_log2, -m_use[0])), p1 = fast_exp2(fmaf(s[n][1], scale_log2, -m_use[0]));
+        const float p2 = fast_exp2(fmaf(s[n][2], scale_log2, -m_use[1])), p3 = fast_exp2(fmaf(s[n][3], scale_log2, -m_use[1]));
         st.l[0] += p0 + p1;
         st.l[1] += p2 + p3;
         p[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
@@ -234,9 +240,9 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
         cp_async_commit();
     };
 
-    issue(kt_begin, 0);
-    cp_async_wait<1>();                      // the query tile has landed
+    cp_async_wait<0>();                      // the query tile has landed
     __syncthreads();
+    issue(kt_begin, 0);
     uint32_t q[HD / 16][4];
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk) {
@@ -251,20 +257,23 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
         lo[r] = p.window > 0 ? max(0, pos[r] - p.window + 1) : 0;
     }
     RowState<HD> st;
+    // positions of the warp's first and last real row: tiles wholly visible to all 16 rows need no mask
+    const int warp_rows = min(rows - warp * 16, 16);
+    const int warp_first = pos0 + warp * 16, warp_last = warp_first + warp_rows - 1;
+    const int warp_lo_last = p.window > 0 ? max(0, warp_last - p.window + 1) : 0;
     for (int kt = kt_begin; kt < kt_end; ++kt) {
         const int stage = (kt - kt_begin) & 1;
-        if (kt + 1 < kt_end) {
-            issue(kt + 1, stage ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        cp_async_wait<0>();                  // tile kt has landed (this thread's share)
+        __syncthreads();                     // ... everyone's; and everyone is done with the other stage
+        if (kt + 1 < kt_end) issue(kt + 1, stage ^ 1);
         __nv_bfloat16* k_tile = kv_tiles + stage * 2 * TILE * HD;
-        // a warp whose rows all lie before this tile's keys has nothing to add
-        if (kt * TILE <= pos0 + min(rows, warp * 16 + 16) - 1)
-            attend_tile<HD>(st, q, k_tile, k_tile + TILE * HD, kt * TILE, pos, lo, p.scale_log2, lane);
-        __syncthreads();
+        const int key0 = kt * TILE;
+        if (warp_rows > 0 && key0 <= warp_last) {           // else: all of the warp's rows lie before this tile
+            if (warp_rows == 16 && key0 + TILE - 1 <= warp_first && key0 >= warp_lo_last)
+                attend_tile<HD, false>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2, lane);
+            else
+                attend_tile<HD, true>(st, q, k_tile, k_tile + TILE * HD, key0, pos, lo, p.scale_log2, lane);
+        }
     }
     // rows' sums over the quad, then write
 #pragma unroll
@@ -290,6 +299,8 @@ template <int HD>
 __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    chain_wait();                                              // the step's key and query come from the kernel before
+    chain_release();
     const int q_begin = p.cu_q[seq];
     if (p.cu_q[seq + 1] - q_begin != 1) return;
     const int ctx = p.ctx_lens[seq];
@@ -337,7 +348,7 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
         }
         const int posv[2] = {pos, pos};
         const int lov[2] = {first_key, first_key};
-        attend_tile<HD>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
+        attend_tile<HD, true>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
@@ -388,6 +399,8 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
 template <int HD>
 __global__ void decode_combine_kernel(AttnParams p) {
     const int seq = blockIdx.y, head = blockIdx.x;
+    chain_wait();
+    chain_release();
     const int q_begin = p.cu_q[seq];
     if (p.cu_q[seq + 1] - q_begin != 1) return;
     const int ctx = p.ctx_lens[seq];
@@ -427,10 +440,9 @@ int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, c
         const int splits = (max_ctx_len + SPLIT - 1) / SPLIT;
         if (splits > p.max_splits) return ts_fail("decode_attention: %d splits needed, scratch holds %d", splits, p.max_splits);
         dim3 grid(splits, p.nkv, p.num_seqs);
-        kernel<<<grid, 128, smem, stream>>>(p);
-        TS_LAUNCH_CHECK("decode_attention");
-        decode_combine_kernel<HD><<<dim3(p.nh, p.num_seqs), HD, 0, stream>>>(p);
-        TS_LAUNCH_CHECK("decode_combine");
+        TS_CHAINED_CHECK("decode_attention", launch_chained(kernel, grid, dim3(128), smem, stream, p));
+        TS_CHAINED_CHECK("decode_combine", launch_chained(decode_combine_kernel<HD>, dim3(p.nh, p.num_seqs), dim3(HD), 0,
+                                                          stream, p));
     }
     return 0;
 }

@@ -80,6 +80,39 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     return scratch[32];
 }
 
+// Programmatic dependent launch.  A kernel launched through launch_chained() may start while the
+// kernel before it on the stream is still running: it may read what no kernel on the stream writes
+// (weights, tables) at once, and must call chain_wait() before it reads anything an earlier kernel
+// produced and before its first write to global memory; chain_wait() returns when every earlier
+// kernel has finished and its writes are visible.  chain_release() lets the next kernel on the
+// stream start in the same way.  Launched normally, both calls do nothing.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool ts_chaining_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ts_chaining_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#define TS_CHAINED_CHECK(name, expr)                                                              \
+    do {                                                                                          \
+        cudaError_t e_ = (expr);                                                                  \
+        if (e_ != cudaSuccess) return ts_fail("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
+    } while (0)
+
 // Geometry of one cache entry inside a layer group's key (or value) pool.  The pool is laid out
 // [page][entry][kv head][token in page][head_dim]; offsets are in elements.
 struct KVGeometry {

@@ -5,6 +5,8 @@ template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
                                  int hidden, int vocab) {
     const int t = blockIdx.x;
+    chain_wait();
+    chain_release();
     int id = ids[t];
     const bool valid = id >= 0 && id < vocab;      // padding rows carry id -1: they get zeros
     const T* src = table + (long long)(valid ? id : 0) * hidden;
@@ -18,12 +20,13 @@ TS_API int ts_embedding(const void* table, const int* ids, void* out, int num_to
     if (num_tokens == 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == TS_F32)
-        embedding_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, ids, (float*)out, hidden, vocab);
+        TS_CHAINED_CHECK("embedding", launch_chained(embedding_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream,
+                                                     (const float*)table, ids, (float*)out, hidden, vocab));
     else if (dtype == TS_BF16)
-        embedding_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids,
-                                                                           (__nv_bfloat16*)out, hidden, vocab);
+        TS_CHAINED_CHECK("embedding", launch_chained(embedding_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0,
+                                                     stream, (const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out,
+                                                     hidden, vocab));
     else
         return ts_fail("embedding: unknown dtype code %d", dtype);
-    TS_LAUNCH_CHECK("embedding");
     return 0;
 }

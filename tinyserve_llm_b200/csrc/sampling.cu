@@ -27,6 +27,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long row_st
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const int r = blockIdx.x;
+    chain_wait();
+    chain_release();
     const float* row = logits + (long long)r * row_stride;
     const float temp = temperatures[r];
     const uint32_t k0 = keys[2 * r], k1 = keys[2 * r + 1];
@@ -68,7 +70,7 @@ TS_API int ts_sample(const float* logits, long long row_stride, const float* tem
     TS_REQUIRE(num_rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d V=%d", num_rows, vocab);
     if (num_rows == 0) return 0;
     const int threads = vocab >= 4096 ? 1024 : 256;
-    sample_kernel<<<num_rows, threads, 0, stream>>>(logits, row_stride, temperatures, keys, out, vocab);
-    TS_LAUNCH_CHECK("sample");
+    TS_CHAINED_CHECK("sample", launch_chained(sample_kernel, dim3(num_rows), dim3(threads), 0, stream, logits, row_stride,
+                                              temperatures, keys, out, vocab));
     return 0;
 }

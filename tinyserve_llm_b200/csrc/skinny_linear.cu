@@ -78,17 +78,34 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
         for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
 
     const int kblocks = K / 32;
-    for (int kb0 = warp * UNROLL; kb0 < kblocks; kb0 += WARPS * UNROLL) {
-        uint4 wl[UNROLL], wh[UNROLL], xv[UNROLL][MT];
+    const int stride = WARPS * UNROLL;
+    // The first weights are asked for before the kernel ahead on the stream has finished: they do
+    // not depend on it.  x does, so it is read after chain_wait().  Inside the loop the next batch
+    // of weights is in flight while the current one is multiplied.
+    uint4 wl[UNROLL], wh[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        const int kb = min(warp * UNROLL + u, kblocks - 1);
+        wl[u] = ld_stream(w_lo + kb * 32);
+        wh[u] = ld_stream(w_hi + kb * 32);
+    }
+    chain_wait();
+    chain_release();
+    for (int kb0 = warp * UNROLL; kb0 < kblocks; kb0 += stride) {
+        uint4 xv[UNROLL][MT], nl[UNROLL], nh[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int kb = kb0 + u;
-            if (kb < kblocks) {
-                wl[u] = ld_stream(w_lo + kb * 32);
-                wh[u] = ld_stream(w_hi + kb * 32);
+            const int kb = min(kb0 + u, kblocks - 1);
 #pragma unroll
-                for (int t = 0; t < MT; ++t)
-                    xv[u][t] = x_ok[t] ? *reinterpret_cast<const uint4*>(x_row[t] + kb * 32) : make_uint4(0, 0, 0, 0);
+            for (int t = 0; t < MT; ++t)
+                xv[u][t] = x_ok[t] ? *reinterpret_cast<const uint4*>(x_row[t] + kb * 32) : make_uint4(0, 0, 0, 0);
+        }
+        if (kb0 + stride < kblocks) {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int kb = min(kb0 + stride + u, kblocks - 1);
+                nl[u] = ld_stream(w_lo + kb * 32);
+                nh[u] = ld_stream(w_hi + kb * 32);
             }
         }
 #pragma unroll
@@ -100,6 +117,11 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
                     mma_bf16(acc[t], wl[u].z, wh[u].z, wl[u].w, wh[u].w, xv[u][t].z, xv[u][t].w);
                 }
             }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            wl[u] = nl[u];
+            wh[u] = nh[u];
         }
     }
 #pragma unroll
@@ -141,9 +163,9 @@ template <int MT, int WARPS, int EPI, typename OUT>
 int launch(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
            cudaStream_t stream) {
     const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
-    skinny_linear_kernel<MT, WARPS, EPI, OUT><<<tiles, WARPS * 32, 0, stream>>>(
-        (const __nv_bfloat16*)W, (const __nv_bfloat16*)x, (OUT*)y, M, N, K, ldx, ldy, inter);
-    TS_LAUNCH_CHECK("skinny_linear");
+    TS_CHAINED_CHECK("skinny_linear", launch_chained(skinny_linear_kernel<MT, WARPS, EPI, OUT>, dim3(tiles),
+                                                     dim3(WARPS * 32), 0, stream, (const __nv_bfloat16*)W,
+                                                     (const __nv_bfloat16*)x, (OUT*)y, M, N, K, ldx, ldy, inter));
     return 0;
 }
 

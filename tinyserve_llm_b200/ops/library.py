@@ -7,6 +7,7 @@ attention: if the shared object cannot be built or loaded, constructing `Ops` ra
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -41,6 +42,12 @@ class Ops:
         self.lib.ts_abi_version.restype = c_int
         self.launches = 0            # kernels of this library launched (or captured into a graph) so far
         self.skinny_max_rows = int(self.lib.ts_skinny_linear_max_rows())
+        # TINYSERVE_B200_CHAINING=0 launches every kernel fully serialised (no programmatic dependent launch)
+        self.set_chaining(os.environ.get("TINYSERVE_B200_CHAINING", "1") != "0")
+
+    def set_chaining(self, enabled: bool) -> None:
+        self.chaining = bool(enabled)
+        self.lib.ts_set_chaining(c_int(1 if enabled else 0))
 
     # ------------------------------------------------------------------ helpers
     def _call(self, name: str, *args) -> None:
