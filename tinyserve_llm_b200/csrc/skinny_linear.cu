@@ -90,7 +90,7 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
         wh[u] = ld_stream(w_hi + kb * 32);
     }
     chain_wait();
-    chain_release();
+    chain_release();      // after the wait: letting later kernels in sooner (before it) slowed the step by a third
     for (int kb0 = warp * UNROLL; kb0 < kblocks; kb0 += stride) {
         uint4 xv[UNROLL][MT], nl[UNROLL], nh[UNROLL];
 #pragma unroll
