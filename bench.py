@@ -148,7 +148,7 @@ def run_ours(args) -> dict:
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(cfg, f)
     steps, warmup = args.steps, max(args.warmup, 3)
-    max_len = CONTEXT + steps + warmup + 64
+    max_len = CONTEXT + steps + warmup + 64 + 512
     pages = 64 * (-(-max_len // PAGE) + 1) + 8
     llm = LLM(folder, SchedulerConfig(max_model_len=max_len, max_num_seqs=64, max_num_batched_tokens=8192,
                                       prefill_chunk=2048, watermark=0.0),
@@ -169,13 +169,16 @@ def run_ours(args) -> dict:
             llm.step()
 
     def finish_all():
+        for s in llm.scheduler.running + llm.scheduler.waiting:      # one more token, then done
+            s.params = SamplingParams(max_tokens=len(s.output_token_ids) + 1, temperature=0.0, ignore_eos=True)
         while llm.scheduler.has_unfinished():
             llm.step()
 
     def device_decode(batch: int, context: int, k: int, w: int):
         """K decode steps timed on the device: graph replay + sampling kernel, no host read in between."""
-        start_decoding(batch, context, w + k + 2)
+        start_decoding(batch, context, w + k + 2 + 512)      # room for the tokens decoded while the others still prefill
         seqs = list(llm.scheduler.running)
+        assert len(seqs) == batch, f"{len(seqs)} of {batch} requests are decoding"
         entries = []
         for s in seqs:                                    # reserve the step's slot as the scheduler would
             cache.extend(s.seq_id, [s.output_token_ids[-1]])
@@ -223,7 +226,7 @@ def run_ours(args) -> dict:
     with ClockSampler() as clocks:
         ms, launches = device_decode(BATCH, CONTEXT, steps, warmup)
         # ---- end to end through the entry point: host token ids in, host token ids out
-        start_decoding(BATCH, CONTEXT, warmup + steps + 2)
+        start_decoding(BATCH, CONTEXT, warmup + steps + 2 + 512)
         for _ in range(warmup):
             llm.step()
         torch.cuda.synchronize()

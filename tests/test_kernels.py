@@ -326,3 +326,30 @@ def test_linear_with_swiglu_epilogue(ops, m, inter, k):
     got = ops.linear_swiglu(x.to(DEV), w.to(DEV)).cpu().double()
     scale = want.abs().max().item()
     torch.testing.assert_close(got, want, atol=scale * 2 ** -7, rtol=2 ** -6)
+
+
+@pytest.mark.parametrize("m, n, k", [(128, 128, 64), (1, 16, 8), (100, 200, 72), (130, 130, 136), (300, 1000, 192),
+                                      (2048, 3072, 2048), (257, 4096, 520), (64, 2048, 8192)])
+def test_tcgen05_matrix_product(ops, m, n, k):
+    """TMA-fed tcgen05 product: tiles that run over the edges of M, N and K, narrow and wide tile shapes."""
+    x, w = rand((m, k), torch.bfloat16, 5), rand((n, k), torch.bfloat16, 6, 0.05)
+    want = x.double() @ w.double().T
+    scale = want.abs().max().item()
+    got = ops.gemm_tcgen05(x.to(DEV), w.to(DEV)).cpu().double()
+    torch.testing.assert_close(got, plain.rnd(want, "bfloat16"), atol=scale * 2 ** -8, rtol=2 ** -7)
+    wide = ops.gemm_tcgen05(x.to(DEV), w.to(DEV), out_dtype=torch.float32).cpu().double()
+    torch.testing.assert_close(wide, want, atol=scale * 1e-5, rtol=1e-4)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+
+
+@pytest.mark.parametrize("m, inter, k", [(33, 64, 64), (100, 176, 72), (64, 8192, 2048), (2048, 8192, 2048), (300, 500, 192)])
+def test_tcgen05_product_with_swiglu_epilogue(ops, m, inter, k):
+    x, w = rand((m, k), torch.bfloat16, 7), rand((2 * inter, k), torch.bfloat16, 8, 0.2)
+    gate_up = plain.rnd(x.double() @ w.double().T, "bfloat16")
+    want = plain.swiglu(gate_up, "bfloat16")
+    got = ops.linear_swiglu(x.to(DEV), w.to(DEV)).cpu().double()
+    scale = want.abs().max().item()
+    torch.testing.assert_close(got, want, atol=scale * 2 ** -7, rtol=2 ** -6)
+    torch.cuda.synchronize()
+    ops.check_device_errors()

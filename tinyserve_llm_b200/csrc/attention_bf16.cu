@@ -8,7 +8,7 @@
 //    max(0, p - window + 1) .. p (attention/torch_paged.py:36-45 of the reference, by positions).
 //  * decode: requests that feed one token.  The g query heads that share a kv head are the rows of
 //    one tile; the keys are cut into splits of 256 (fixed by key index, so the sums do not depend on
-//    the batch); a CTA takes one split, each of its 4 warps one tile of 64 keys; warps merge in
+//    the batch); a CTA takes one split, each of its warps one tile of 64 keys; warps merge in
 //    shared memory and write (max, sum, output) partials to scratch; a second kernel combines the
 //    splits of each head.
 //
@@ -19,7 +19,11 @@
 namespace {
 
 constexpr int TILE = 64;           // keys per tile, queries per prefill CTA
-constexpr int SPLIT = 256;         // keys per decode split
+#ifndef TS_DECODE_WARPS
+#define TS_DECODE_WARPS 4
+#endif
+constexpr int DW = TS_DECODE_WARPS;  // warps of a decode CTA, one tile of 64 keys each
+constexpr int SPLIT = DW * TILE;    // keys per decode split
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -296,7 +300,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
 
 // ------------------------------------------------------------------------------------------------ decode
 template <int HD>
-__global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
+__global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     chain_wait();                                              // the step's key and query come from the kernel before
@@ -356,8 +360,8 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
         }
     }
     __syncthreads();                                           // tiles are done with: reuse the memory for the merge
-    float* merge_o = reinterpret_cast<float*>(smem_raw);       // [4 warps][16 rows][HD]
-    float* merge_ml = merge_o + 4 * 16 * HD;                   // [4 warps][16 rows][2]
+    float* merge_o = reinterpret_cast<float*>(smem_raw);       // [warps][16 rows][HD]
+    float* merge_ml = merge_o + DW * 16 * HD;                   // [warps][16 rows][2]
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + r * 8;
@@ -374,14 +378,14 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(AttnParams p) {
     }
     __syncthreads();
     // rows 0..g-1: merge the four warps in order, one thread per (row, dim)
-    for (int i = tid; i < g * HD; i += 128) {
+    for (int i = tid; i < g * HD; i += DW * 32) {
         const int row = i / HD, d = i % HD;
         float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) m = fmaxf(m, merge_ml[(w * 16 + row) * 2]);
+        for (int w = 0; w < DW; ++w) m = fmaxf(m, merge_ml[(w * 16 + row) * 2]);
         float l = 0.f, o = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < DW; ++w) {
             const float mw = merge_ml[(w * 16 + row) * 2];
             const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
             l += merge_ml[(w * 16 + row) * 2 + 1] * f;
@@ -432,15 +436,15 @@ int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, c
         TS_LAUNCH_CHECK("prefill_attention");
     }
     if (min_q_len <= 1) {
-        const size_t tiles = (size_t)4 * (16 + 2 * TILE) * HD * sizeof(__nv_bfloat16);
-        const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
+        const size_t tiles = (size_t)DW * (16 + 2 * TILE) * HD * sizeof(__nv_bfloat16);
+        const size_t merge = (size_t)(DW * 16 * HD + DW * 16 * 2) * sizeof(float);
         const size_t smem = tiles > merge ? tiles : merge;
         auto kernel = decode_attention_kernel<HD>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         const int splits = (max_ctx_len + SPLIT - 1) / SPLIT;
         if (splits > p.max_splits) return ts_fail("decode_attention: %d splits needed, scratch holds %d", splits, p.max_splits);
         dim3 grid(splits, p.nkv, p.num_seqs);
-        TS_CHAINED_CHECK("decode_attention", launch_chained(kernel, grid, dim3(128), smem, stream, p));
+        TS_CHAINED_CHECK("decode_attention", launch_chained(kernel, grid, dim3(DW * 32), smem, stream, p));
         TS_CHAINED_CHECK("decode_combine", launch_chained(decode_combine_kernel<HD>, dim3(p.nh, p.num_seqs), dim3(HD), 0,
                                                           stream, p));
     }

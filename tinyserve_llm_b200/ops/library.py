@@ -41,6 +41,7 @@ class Ops:
         self.lib.ts_last_error.restype = ctypes.c_char_p
         self.lib.ts_abi_version.restype = c_int
         self.launches = 0            # kernels of this library launched (or captured into a graph) so far
+        self._error_word: torch.Tensor | None = None
         self.skinny_max_rows = int(self.lib.ts_skinny_linear_max_rows())
         # TINYSERVE_B200_CHAINING=0 launches every kernel fully serialised (no programmatic dependent launch)
         self.set_chaining(os.environ.get("TINYSERVE_B200_CHAINING", "1") != "0")
@@ -198,6 +199,38 @@ class Ops:
             return torch.mm(x, weight.t(), out_dtype=out_dtype)
         return torch.mm(x, weight.t())
 
+    def gemm_tcgen05(self, x: torch.Tensor, weight: torch.Tensor, *, swiglu: bool = False,
+                     out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """
+        x [M, K] . weight[N, K]^T on tcgen05 tensor cores with TMA-fed shared memory; `swiglu` stores
+        silu(gate) * up of the two halves of the weight's rows instead ([M, N / 2]).
+        """
+        self._check(x, "x", torch.bfloat16, 2)
+        self._check(weight, "weight", torch.bfloat16, 2)
+        M, K = x.shape
+        N = weight.shape[0]
+        if weight.shape[1] != K:
+            raise KernelError(f"gemm_tcgen05: x has {K} columns, the weight {weight.shape[1]}")
+        out_dtype = out_dtype or torch.bfloat16
+        cols = N // 2 if swiglu else N
+        out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
+        if M == 0:
+            return out
+        if self._error_word is None:
+            self._error_word = torch.zeros((1,), dtype=torch.int32).pin_memory()    # device-visible host memory
+        self._call("ts_gemm_tcgen05", _ptr(weight), _ptr(x), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(K),
+                   c_longlong(cols), c_int(1 if swiglu else 0), c_int(_DTYPE_CODE[out_dtype]),
+                   c_void_p(self._error_word.data_ptr()), _stream())
+        return out
+
+    def check_device_errors(self) -> None:
+        """Raises if a kernel's bounded wait ran out (the word lives in pinned host memory: no sync needed)."""
+        if self._error_word is not None and int(self._error_word[0]) != 0:
+            code = int(self._error_word[0])
+            self._error_word[0] = 0
+            where = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, "unknown")
+            raise KernelError(f"gemm_tcgen05: a {where} wait on an mbarrier ran out of time (code {code})")
+
     def _skinny(self, x: torch.Tensor, weight: torch.Tensor) -> bool:
         """A few rows of bfloat16 x (a decode step): the engine's own weight-streaming kernel takes them."""
         return (x.dtype == torch.bfloat16 and 0 < x.shape[0] <= self.skinny_max_rows and x.shape[1] % 32 == 0
@@ -210,6 +243,11 @@ class Ops:
         if gate_up_weight.shape[0] % 2 or x.shape[1] != gate_up_weight.shape[1]:
             raise KernelError("linear_swiglu: the weight must hold gate and up halves over x's columns")
         if not self._skinny(x, gate_up_weight):
+            if x.dtype == torch.bfloat16 and self.lib.ts_gemm_tcgen05_supported(
+                    _ptr(gate_up_weight), _ptr(x), c_int(x.shape[0]), c_int(gate_up_weight.shape[0]), c_int(x.shape[1]),
+                    c_longlong(x.shape[1])):
+                # tcgen05 product with the activation in its epilogue: the [M, 2I] product never reaches memory
+                return self.gemm_tcgen05(x, gate_up_weight, swiglu=True)
             return self.silu_mul(self.linear(x, gate_up_weight))
         inter = gate_up_weight.shape[0] // 2
         out = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
