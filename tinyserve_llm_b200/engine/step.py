@@ -189,26 +189,32 @@ class StepRunner:
         sections = [ids, positions, seq_of_token, cu_q, ctx_lens, rows, slots]
         for g in range(groups):
             flat: list[int] = []
+            width = widths[g]
             for e in entries:
                 t = mgr.seqs[e.seq_id].tables[g]
-                if len(t) > widths[g]:
-                    raise ValueError(f"request {e.seq_id!r} holds {len(t)} pages; the step was built for {widths[g]}")
+                if len(t) > width:
+                    raise ValueError(f"request {e.seq_id!r} holds {len(t)} pages; the step was built for {width}")
                 flat.extend(t)
-                flat.extend([-1] * (widths[g] - len(t)))
-            flat.extend([-1] * (widths[g] * (S - len(entries))))
+                if len(t) < width:
+                    flat.extend([-1] * (width - len(t)))
+            if S > len(entries):
+                flat.extend([-1] * (width * (S - len(entries))))
             sections.append(flat)
-        offsets, total = [], 0
+        # one list, one conversion, one copy into the pinned buffer, one copy to the device
+        offsets, packed = [], []
         for sec in sections:
-            offsets.append(total)
-            total += _pad4(max(len(sec), 1))
+            offsets.append(len(packed))
+            packed.extend(sec)
+            pad = _pad4(max(len(sec), 1)) - len(sec)
+            if pad:
+                packed.extend([0] * pad)
+        total = len(packed)
         if self._staging is None or self._staging.numel() < total:
             self._staging = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
         else:
             self._staged.synchronize()                  # the previous step's copy has read the buffer
         host = self._staging
-        for off, sec in zip(offsets, sections):
-            if sec:
-                host[off:off + len(sec)] = torch.tensor(sec, dtype=torch.int32)
+        host[:total] = torch.tensor(packed, dtype=torch.int32)
         if into is None:
             dev = host[:total].to(self.device, non_blocking=True)
         else:
@@ -253,7 +259,7 @@ class StepRunner:
         if captured is None:
             captured = self._capture(entries, size)
         else:
-            self._pack(entries, pad_to=size, widths=captured.widths, into=captured.index_buffer)
+            self._refill(entries, size, captured)
             captured.graph.replay()
             self.model.rt.ops.launches += captured.launches
         self.graph_replays += 1
@@ -263,6 +269,50 @@ class StepRunner:
         if not wanted:
             return captured.logits[:0]
         return captured.logits.index_select(0, torch.tensor(wanted, dtype=torch.int64, device=self.device))
+
+    def _refill(self, entries: Sequence[StepEntry], size: int, captured: _DecodeGraph) -> None:
+        """
+        The index data of a decode step straight into the graph's static buffer: the same layout
+        `_pack` produces for `pad_to=size`, without building a context nobody reads.
+        """
+        seqs = self.manager.seqs
+        n, extra = len(entries), size - len(entries)
+        states = [seqs[e.seq_id] for e in entries]
+        first = [st.committed for st in states]
+        packed: list[int] = []
+
+        def section(values: list[int]) -> None:
+            packed.extend(values)
+            pad = _pad4(max(len(values), 1)) - len(values)
+            if pad:
+                packed.extend([0] * pad)
+
+        section([e.tokens[0] for e in entries] + [0] * extra)                    # token ids
+        section(first + [0] * extra)                                              # positions
+        section(list(range(n)) + [-1] * extra)                                    # request of each token
+        section(list(range(size + 1)))                                            # offsets: one token each
+        section([f + 1 for f in first] + [0] * extra)                             # lengths after this step
+        section(list(range(size)))                                                # every row's logits
+        section([st.state_slot for st in states] + [-1] * extra)                  # state slots
+        for g, width in enumerate(captured.widths):
+            flat: list[int] = []
+            for st in states:
+                t = st.tables[g]
+                if len(t) > width:
+                    raise ValueError(f"a request holds {len(t)} pages; the decode graph was built for {width}")
+                flat.extend(t)
+                if len(t) < width:
+                    flat.extend([-1] * (width - len(t)))
+            flat.extend([-1] * (width * extra))
+            section(flat)
+        total = len(packed)
+        if self._staging is None or self._staging.numel() < total:
+            self._staging = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
+        else:
+            self._staged.synchronize()
+        self._staging[:total] = torch.tensor(packed, dtype=torch.int32)
+        captured.index_buffer[:total].copy_(self._staging[:total], non_blocking=True)
+        self._staged.record()
 
     def _capture(self, entries: Sequence[StepEntry], size: int) -> _DecodeGraph:
         widths = list(self._graph_widths)

@@ -43,12 +43,11 @@ class Sampler:
             return []
         if rows is not None and list(rows) != list(range(logits.shape[0])):
             logits = logits.index_select(0, torch.tensor(list(rows), dtype=torch.int64, device=logits.device))
-        packed = torch.empty((count, 3), dtype=torch.int32)
-        temps = torch.tensor(list(temperatures), dtype=torch.float32)
-        packed[:, 0] = temps.view(torch.int32)
-        keys = [draw_key(self.seed, *d) if t > 0 else (0, 0) for d, t in zip(draws, temperatures)]
-        packed[:, 1:] = torch.tensor(keys, dtype=torch.int32)
-        dev = packed.to(self.device, non_blocking=True)
-        temps_dev = dev[:, 0].contiguous().view(torch.float32)
-        keys_dev = dev[:, 1:].contiguous()
+        bits, keys = [], []
+        for d, t in zip(draws, temperatures):
+            bits.append(struct.unpack("<i", struct.pack("<f", t))[0])
+            keys.extend(draw_key(self.seed, *d) if t > 0 else (0, 0))
+        dev = torch.tensor(bits + keys, dtype=torch.int32).to(self.device, non_blocking=True)   # one small copy
+        temps_dev = dev[:count].view(torch.float32)
+        keys_dev = dev[count:].view(count, 2)
         return self.ops.sample(logits.contiguous(), temps_dev, keys_dev).tolist()
