@@ -48,6 +48,15 @@ MODEL = {
     "mlp_bias": False,
     "torch_dtype": "bfloat16",
 }
+# BASELINE.json configs[3] and configs[4]: Llama 3.2 3B and Llama 3.1 8B (--model 3b / 8b)
+MODELS = {
+    "1b": ("Llama-3.2-1B", {}, 2048),
+    "3b": ("Llama-3.2-3B", {"hidden_size": 3072, "num_hidden_layers": 28, "num_attention_heads": 24, "head_dim": 128}, 2048),
+    "8b": ("Llama-3.1-8B", {"hidden_size": 4096, "num_hidden_layers": 32, "num_attention_heads": 32, "head_dim": 128,
+                            "intermediate_size": 14336, "tie_word_embeddings": False,
+                            "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                             "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}}, 4096),
+}
 FULL_LAYERS = 16
 BATCH = 8
 CONTEXT = 4096            # benchmark context length of the configuration
@@ -142,14 +151,17 @@ def run_ours(args) -> dict:
     from tinyserve_llm_b200 import LLM, CacheConfig, SamplingParams, SchedulerConfig
     from tinyserve_llm_b200.engine.step import StepEntry
 
-    layers = args.layers
-    cfg = dict(MODEL, num_hidden_layers=layers)
+    model_name, overrides, point_context = MODELS[args.model]
+    cfg = dict(MODEL, **overrides)
+    full_layers = cfg["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg["num_hidden_layers"] = layers
     folder = tempfile.mkdtemp(prefix="bench_model_")
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(cfg, f)
     steps, warmup = args.steps, max(args.warmup, 3)
     max_len = CONTEXT + steps + warmup + 64 + 512
-    pages = 64 * (-(-max_len // PAGE) + 1) + 8
+    pages = 66 * (-(-max_len // PAGE) + 1) + 16
     llm = LLM(folder, SchedulerConfig(max_model_len=max_len, max_num_seqs=64, max_num_batched_tokens=8192,
                                       prefill_chunk=2048, watermark=0.0),
               CacheConfig(block_size=PAGE, caching=False), dtype="bfloat16", num_blocks=pages, seed=0,
@@ -240,15 +252,40 @@ def run_ours(args) -> dict:
     h2d = (graph.index_buffer.numel() * 4 if graph else 0) + BATCH * 3 * 4
     points = {}
     for b in (1, 8, 64):
-        pms, _ = device_decode(b, POINT_CONTEXT, max(10, steps // 2), 3)
+        pms, _ = device_decode(b, point_context, max(10, steps // 2), 3)
         points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+    # a mixed step: 64 requests decoding beside one 2,048-token prompt portion
+    start_decoding(64, point_context, 8 + 512)
+    mixed_entries = []
+    for sq in llm.scheduler.running:
+        cache.extend(sq.seq_id, [sq.output_token_ids[-1]])
+        mixed_entries.append(StepEntry(sq.seq_id, [sq.output_token_ids[-1]], [0]))
+    chunk = prompts(1, PREFILL_TOKENS)[0]
+    assert cache.admit(("mixed", 0), chunk)
+    mixed_entries.append(StepEntry(("mixed", 0), chunk, [PREFILL_TOKENS - 1]))
+    for _ in range(2):
+        runner.step(mixed_entries)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(5):
+        runner.step(mixed_entries)
+    end.record()
+    torch.cuda.synchronize()
+    mixed_ms = begin.elapsed_time(end) / 5
+    cache.commit(("mixed", 0), PREFILL_TOKENS)
+    cache.release(("mixed", 0))
+    for sq in list(llm.scheduler.running):
+        cache.commit(sq.seq_id, 1)
+        sq.output_token_ids.append(0)
+    finish_all()
 
     value = BATCH / ms * 1e3
     moved = weight_bytes(cfg, layers) + kv_bytes(cfg, layers, BATCH, CONTEXT)
     achieved = moved / (ms * 1e-3) / 1e9
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
     record = {
-        "metric": "decode tok/s at batch 8 (Llama 3.2 1B, bf16, one B200)",
+        "metric": f"decode tok/s at batch 8 ({model_name}, bf16, one B200)",
         "value": round(value, 1),
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -262,11 +299,11 @@ def run_ours(args) -> dict:
         "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)",
         "impl": "ours",
         "config": {
-            "model": "Llama-3.2-1B", "layers": layers, "layers_of_model": FULL_LAYERS, "hidden_size": cfg["hidden_size"],
+            "model": model_name, "layers": layers, "layers_of_model": full_layers, "hidden_size": cfg["hidden_size"],
             "intermediate_size": cfg["intermediate_size"], "num_attention_heads": cfg["num_attention_heads"],
             "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "vocab_size": cfg["vocab_size"], "global_batch": BATCH, "seq_len": CONTEXT,
-            "points_context_len": POINT_CONTEXT, "prefill_tokens": PREFILL_TOKENS, "page_tokens": PAGE,
+            "points_context_len": point_context, "prefill_tokens": PREFILL_TOKENS, "page_tokens": PAGE,
             "parallelism": "single GPU", "cuda_graphs": bool(graph), "l2": "inputs larger than L2 (weights 2.5 GB per step)",
             "peaks": peak_kind,
         },
@@ -275,6 +312,8 @@ def run_ours(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4)},
         "points": points,
+        "mixed": {"decodes": 64, "prefill_tokens": PREFILL_TOKENS, "ms": round(mixed_ms, 3),
+                  "value": round((64 + PREFILL_TOKENS) / mixed_ms * 1e3, 1), "unit": "tokens/s"},
         "e2e": {"value": round(BATCH * steps / e2e_seconds, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": BATCH * 4},
         "gpu_launches": launches,
@@ -299,7 +338,7 @@ def run_reference(args) -> dict:
         from tinyserve_llm_b200.weights import write_random_model
     except Exception as exc:                                  # noqa: BLE001
         return {"impl": "reference", "unavailable": f"import failed: {type(exc).__name__}: {exc}"[:300]}
-    layers = args.layers
+    layers = args.layers or FULL_LAYERS
     cfg = dict(MODEL, num_hidden_layers=layers)
     steps, warmup = args.steps, max(args.warmup, 3)
     folder = tempfile.mkdtemp(prefix="bench_ref_model_")
@@ -338,7 +377,8 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (named in config)")
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config); 0: all")
+    parser.add_argument("--model", choices=sorted(MODELS), default="1b", help="layer sizes: Llama 3.2 1B (default), 3B, 3.1 8B")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (run with --gpus 1)")
