@@ -353,3 +353,45 @@ def test_tcgen05_product_with_swiglu_epilogue(ops, m, inter, k):
     torch.testing.assert_close(got, want, atol=scale * 2 ** -7, rtol=2 ** -6)
     torch.cuda.synchronize()
     ops.check_device_errors()
+
+
+@pytest.mark.parametrize("nh, nkv, page", [(8, 2, 64), (32, 8, 256), (5, 5, 128), (3, 1, 64)])
+def test_tcgen05_prompt_attention(ops, nh, nkv, page):
+    """
+    Prompt portions on the tcgen05 kernel (TMA tiles, S and O in tensor memory): whole prompts of
+    several query tiles, a portion over a long cached prefix that ends inside a page, a two-token
+    portion, beside requests that decode; against the plain reference and against the mma.sync
+    kernel on the same inputs.  Pools are poisoned with NaN: the unwritten tail of a last page must
+    not reach the result.
+    """
+    hd = 64
+    q_lens = [300, 1, 130, 2, 128, 1]
+    ctx_lens = [300, 700, 1000, 2, 128, 65]
+    ctx = make_ctx(q_lens, ctx_lens)
+    tables, at = [], 0
+    for c in ctx_lens:
+        n = -(-c // page)
+        tables.append(list(range(at + n - 1, at - 1, -1)))
+        at += n
+    binding = make_binding(at + 1, 2, nkv, page, hd, torch.bfloat16, tables, entry=1)
+    keys = [rand((c, nkv, hd), torch.bfloat16, 40 + s) for s, c in enumerate(ctx_lens)]
+    values = [rand((c, nkv, hd), torch.bfloat16, 50 + s) for s, c in enumerate(ctx_lens)]
+    for s in range(len(ctx_lens)):
+        fill_cache(binding, s, keys[s], values[s], entry=1)
+    T = ctx.num_tokens
+    qkv = rand((T, (nh + 2 * nkv) * hd), torch.bfloat16, 12)
+    qkv[5, :hd] = (keys[0][2, 0].float() * 3).to(torch.bfloat16)      # token 5 of the first prompt attends to key 2 above all
+    scale = hd ** -0.5
+    assert ops.tcgen05_attention
+    got = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0).cpu().double().view(T, nh, hd)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    want = plain_paged_attention(qkv[:, : nh * hd].view(T, nh, hd).double(), keys, values, ctx_lens, q_lens, scale, 0)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, plain.rnd(want, "bfloat16"), **tol(torch.bfloat16, 2))
+    ops.tcgen05_attention = False
+    try:
+        legacy = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0).cpu().double().view(T, nh, hd)
+    finally:
+        ops.tcgen05_attention = True
+    torch.testing.assert_close(got, legacy, **tol(torch.bfloat16, 2))

@@ -237,6 +237,7 @@ class StepRunner:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """float32 [wanted places, vocab] on the device, in the order of the entries and of their `want`."""
         self._validate(entries)
+        self.model.rt.ops.check_device_errors()      # a bounded wait that ran out in an earlier step (host-visible word)
         if self.cuda_graphs and len(entries) <= self.max_decode_batch and all(len(e.tokens) == 1 for e in entries):
             return self._decode_step(entries)
         ctx = self._pack(entries)

@@ -45,6 +45,8 @@ class Ops:
         self.skinny_max_rows = int(self.lib.ts_skinny_linear_max_rows())
         # TINYSERVE_B200_CHAINING=0 launches every kernel fully serialised (no programmatic dependent launch)
         self.set_chaining(os.environ.get("TINYSERVE_B200_CHAINING", "1") != "0")
+        # TINYSERVE_B200_PREFILL=mma keeps prompt attention on the mma.sync kernel (the tcgen05 one is the default)
+        self.tcgen05_attention = os.environ.get("TINYSERVE_B200_PREFILL", "tcgen05") != "mma"
 
     def set_chaining(self, enabled: bool) -> None:
         self.chaining = bool(enabled)
@@ -142,6 +144,22 @@ class Ops:
                 and self.lib.ts_attention_bf16_supported(c_int(hd), c_int(binding.page_tokens), c_int(nh), c_int(nkv))):
             num_seqs = ctx.ctx_lens.shape[0]
             scratch, floats = None, 0
+            max_q_len = ctx.max_q_len
+            if (max_q_len > 1 and self.tcgen05_attention and self.lib.ts_attention_tcgen05_supported(
+                    c_int(hd), c_int(binding.page_tokens), c_int(nh), c_int(nkv), c_int(window))):
+                # prompt portions on the tcgen05 kernel; requests that feed one token stay with the split-key kernels
+                per_entry = nkv * binding.page_tokens * hd
+                if self._error_word is None:
+                    self._error_word = torch.zeros((1,), dtype=torch.int32).pin_memory()
+                self._call("ts_prefill_attention_tcgen05", _ptr(qkv), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
+                           c_int(binding.num_pages), c_int(binding.page_stride // per_entry),
+                           c_int(binding.entry_offset // per_entry), c_int(binding.page_tokens), _ptr(binding.block_table),
+                           c_int(binding.table_width), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), c_int(num_seqs),
+                           c_int(qkv.shape[0]), c_int(max_q_len), c_int(nh), c_int(nkv), c_int(hd), c_float(scale),
+                           c_void_p(self._error_word.data_ptr()), _stream())
+                if ctx.min_q_len > 1:
+                    return out
+                max_q_len = 1
             if ctx.min_q_len <= 1:
                 self.lib.ts_attention_bf16_scratch_floats.restype = c_longlong
                 floats = self.lib.ts_attention_bf16_scratch_floats(c_int(num_seqs), c_int(nh), c_int(hd),
@@ -153,11 +171,11 @@ class Ops:
             self._call("ts_paged_attention_bf16", _ptr(qkv), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
                        c_longlong(binding.page_stride), c_longlong(binding.entry_offset), c_int(binding.page_tokens),
                        c_int(binding.num_pages), _ptr(binding.block_table), c_int(binding.table_width),
-                       _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), c_int(num_seqs), c_int(ctx.max_q_len),
-                       c_int(ctx.min_q_len), c_int(ctx.max_ctx_len), c_int(nh), c_int(nkv), c_int(hd), c_float(scale),
-                       c_int(window), _ptr(scratch), c_longlong(floats), _stream())
+                       _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), c_int(num_seqs), c_int(max_q_len),
+                       c_int(min(ctx.min_q_len, max_q_len)), c_int(ctx.max_ctx_len), c_int(nh), c_int(nkv), c_int(hd),
+                       c_float(scale), c_int(window), _ptr(scratch), c_longlong(floats), _stream())
             if ctx.min_q_len <= 1:
-                self.launches += 1 if ctx.max_q_len <= 1 else 2      # decode + combine (+ prefill) in one call
+                self.launches += 1 if max_q_len <= 1 else 2          # decode + combine (+ prefill) in one call
             return out
         self._call("ts_paged_attention_generic", _ptr(qkv), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
                    c_longlong(binding.page_stride), c_longlong(binding.entry_offset), c_int(binding.page_tokens),
