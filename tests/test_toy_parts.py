@@ -176,3 +176,81 @@ def test_run_list_mistakes_are_refused():
                         ((RunEntry(7, 0),), "names block 7")):
         with pytest.raises(ValueError, match=needle):
             DecoderModel(dataclasses.replace(spec, run=run), tensors, rt)
+
+
+@pytest.mark.parametrize("dtype, hd, page", [(torch.float32, 16, 16), (torch.bfloat16, 64, 64)])
+def test_window_layers_have_pages_of_their_own_and_give_them_back(dtype, hd, page):
+    """
+    A toy model whose second layer sees only the last `window` keys: its cache entry lands in a layer
+    group of its own, whose pages are given back as the window passes and are taken again, while the
+    full-attention layer keeps all of its pages.  Logits equal the plain implementation with the
+    same window, in portions that cross the window's edge and token by token.
+    """
+    import plain_llama as plain
+    from tinyserve_llm_b200.config.spec import (AttentionSpec, BlockSpec, GatedMLPSpec, ModelSpec, RMSNormSpec,
+                                                RotarySpec, RunEntry)
+    from tinyserve_llm_b200.engine.loading import build_cache
+    from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
+    from tinyserve_llm_b200.ops import get_ops
+    from tinyserve_llm_b200.parts.base import Runtime
+    from tinyserve_llm_b200.parts.model import DecoderModel, declared_tensors
+    from tinyserve_llm_b200.weights import random_tensors
+
+    hidden, heads, kv, inter, vocab, window, length = 64, 2, 1, 96, 97, 40, 5 * page + 9
+    rotary = RotarySpec(head_dim=hd, theta=10000.0, max_positions=512)
+    full = AttentionSpec(hidden_size=hidden, num_heads=heads, num_kv_heads=kv, head_dim=hd, scale=hd ** -0.5, position=rotary)
+    local = AttentionSpec(hidden_size=hidden, num_heads=heads, num_kv_heads=kv, head_dim=hd, scale=hd ** -0.5, window=window,
+                          position=rotary)
+    mlp, norm = GatedMLPSpec(hidden_size=hidden, intermediate_size=inter), RMSNormSpec(size=hidden, eps=1e-5)
+    blocks = (BlockSpec("pre_norm", full, mlp, norm, norm, prefix="layers.0."),
+              BlockSpec("pre_norm", local, mlp, norm, norm, prefix="layers.1."))
+    spec = ModelSpec("ToyWindow", vocab, hidden, blocks, (RunEntry(0, 0), RunEntry(1, 1)), norm, "embed.weight",
+                     "final_norm.", None, 512, -1)
+    tensors = dict(random_tensors(declared_tensors(spec), 3, std=0.08, unit_std=0.2))
+    device = torch.device("cuda", torch.cuda.current_device())
+    model = DecoderModel(spec, {k: v.to(device) for k, v in tensors.items()}, Runtime(dtype=dtype, device=device, ops=get_ops()))
+    pages_full = -(-length // page) + 1
+    layout, manager, storage = build_cache(model, page, pages_full)
+    assert [(g.entries, g.window) for g in layout.groups] == [((0,), 0), ((1,), window)] and not manager.caching
+    runner = StepRunner(model, manager, storage)
+
+    ids = torch.randint(0, vocab, (length,), generator=torch.Generator().manual_seed(5)).tolist()
+    act = "float32" if dtype == torch.float32 else "bfloat16"
+    cfg = {"num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd, "hidden_size": hidden,
+           "rope_theta": 10000.0, "max_position_embeddings": 512}
+    w = {k: v.double() for k, v in tensors.items()}
+    x, residual = plain.rnd(w["embed.weight"][torch.tensor(ids)], act), None
+    for layer, win in ((0, 0), (1, window)):
+        lw = {k[len(f"layers.{layer}."):]: v for k, v in w.items() if k.startswith(f"layers.{layer}.")}
+        if residual is None:
+            n, residual = plain.rms_norm(x, lw["input_layernorm.weight"], 1e-5, act), x
+        else:
+            n, residual = plain.add_rms_norm(x, residual, lw["input_layernorm.weight"], 1e-5, act)
+        a, _ = plain.attention_block(cfg, lw, n, torch.arange(length), act, None, win)
+        n, residual = plain.add_rms_norm(a, residual, lw["post_attention_layernorm.weight"], 1e-5, act)
+        x = plain.mlp_block(lw, n, act)
+    want = plain.add_rms_norm(x, residual, w["final_norm.weight"], 1e-5, act)[0] @ w["embed.weight"].T
+
+    got, pos = [], 0
+    for n in [window - 3, 2, page + 1, 1, 1, 30, 1] + [1] * 400:
+        n = min(n, length - pos)
+        if n == 0:
+            break
+        tokens = ids[pos:pos + n]
+        if "w" in manager.seqs:
+            manager.extend("w", tokens)
+        else:
+            assert manager.admit("w", tokens)
+        got.append(runner.step([StepEntry("w", tokens, list(range(n)))]).cpu().double())
+        manager.commit("w", n)
+        pos += n
+    tolerance = dict(atol=2e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=0.012 * want.abs().max().item(), rtol=0.0)
+    torch.testing.assert_close(torch.cat(got), want, **tolerance)
+    table_full, table_local = manager.block_table("w", 0), manager.block_table("w", 1)
+    assert all(p >= 0 for p in table_full) and len(table_full) == -(-length // page)
+    passed = (length - window + 1) // page
+    assert table_local[:passed] == [-1] * passed and all(p >= 0 for p in table_local[passed:])
+    assert manager.counters.window_releases == passed
+    assert manager.available_pages()[1] > manager.available_pages()[0]
+    manager.release("w")
+    assert manager.stats().pages_in_use == 0
