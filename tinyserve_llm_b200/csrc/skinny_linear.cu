@@ -38,26 +38,27 @@ __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
-// MT: tiles of 8 rows of x; WARPS: warps per CTA (the split of K); UNROLL: k-blocks in flight per warp.
-template <int MT, int WARPS, int EPI, typename OUT>
-__global__ void __launch_bounds__(WARPS * 32)
+// MT: tiles of 8 rows of x; WARPS: warps per CTA (the split of K); UNROLL: k-blocks a warp has in
+// flight per batch (two batches are in flight); MINB: CTAs per SM the register budget is held to.
+template <int MT, int WARPS, int EPI, typename OUT, int UNROLL, int MINB>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
 skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x, OUT* __restrict__ y,
                      int M, int N, int K, long long ldx, long long ldy, int inter) {
-    constexpr int UNROLL = 4;
+    constexpr int ROWS = 16;                          // output rows of a CTA (8 pairs with the SwiGLU epilogue)
     __shared__ float partial[WARPS][MT][32][4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, c = lane & 3;
-    // the two rows of W this thread streams (fragment rows r and r + 8)
+    // the rows of W this thread streams (fragment rows r and r + 8)
     long long row_lo, row_hi;
-    int rows_valid;                                   // output rows this CTA really has (<= 16, or <= 8 pairs)
+    int rows_valid;
     if (EPI == EPI_SWIGLU) {
         const int base = blockIdx.x * 8;
         rows_valid = min(8, inter - base);
         row_lo = base + min(r, rows_valid - 1);
         row_hi = (long long)inter + base + min(r, rows_valid - 1);
     } else {
-        const int base = blockIdx.x * 16;
-        rows_valid = min(16, N - base);
+        const int base = blockIdx.x * ROWS;
+        rows_valid = min(ROWS, N - base);
         row_lo = base + min(r, rows_valid - 1);
         row_hi = base + min(r + 8, rows_valid - 1);
     }
@@ -85,17 +86,19 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     uint4 wl[UNROLL], wh[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-        const int kb = min(warp * UNROLL + u, kblocks - 1);
+        const int kb = min(u * WARPS + warp, kblocks - 1);
         wl[u] = ld_stream(w_lo + kb * 32);
         wh[u] = ld_stream(w_hi + kb * 32);
     }
     chain_wait();
     chain_release();      // after the wait: letting later kernels in sooner (before it) slowed the step by a third
-    for (int kb0 = warp * UNROLL; kb0 < kblocks; kb0 += stride) {
+    // warp w takes the k-blocks w, w + WARPS, w + 2 WARPS, ... in that order whatever UNROLL is, so
+    // a row's sum does not depend on the variant that the number of rows of x selects
+    for (int kb0 = warp; kb0 < kblocks; kb0 += stride) {
         uint4 xv[UNROLL][MT], nl[UNROLL], nh[UNROLL];
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int kb = min(kb0 + u, kblocks - 1);
+            const int kb = min(kb0 + u * WARPS, kblocks - 1);
 #pragma unroll
             for (int t = 0; t < MT; ++t)
                 xv[u][t] = x_ok[t] ? *reinterpret_cast<const uint4*>(x_row[t] + kb * 32) : make_uint4(0, 0, 0, 0);
@@ -103,14 +106,14 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
         if (kb0 + stride < kblocks) {
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                const int kb = min(kb0 + stride + u, kblocks - 1);
+                const int kb = min(kb0 + stride + u * WARPS, kblocks - 1);
                 nl[u] = ld_stream(w_lo + kb * 32);
                 nh[u] = ld_stream(w_hi + kb * 32);
             }
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            if (kb0 + u < kblocks) {
+            if (kb0 + u * WARPS < kblocks) {
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
                     mma_bf16(acc[t], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv[u][t].x, xv[u][t].y);
@@ -148,51 +151,65 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
             }
         }
     } else {
-        for (int i = threadIdx.x; i < MT * 32 * 4; i += WARPS * 32) {
-            const int t = i / 128, l = (i / 4) % 32, e = i % 4;
+        constexpr int PER = 4;
+        for (int i = threadIdx.x; i < MT * 32 * PER; i += WARPS * 32) {
+            const int t = i / (32 * PER), l = (i / PER) % 32, e = i % PER;
             float v = 0.f;
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) v += partial[w][t][l][e];
             const int row = (l >> 2) + ((e >> 1) << 3), token = t * 8 + ((l & 3) << 1) + (e & 1);
-            if (row < rows_valid && token < M) store_out<OUT>(y + (long long)token * ldy + blockIdx.x * 16 + row, v);
+            if (row < rows_valid && token < M) store_out<OUT>(y + (long long)token * ldy + blockIdx.x * ROWS + row, v);
         }
     }
 }
 
-template <int MT, int WARPS, int EPI, typename OUT>
+template <int MT, int WARPS, int EPI, typename OUT, int UNROLL, int MINB>
 int launch(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
            cudaStream_t stream) {
     const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
-    TS_CHAINED_CHECK("skinny_linear", launch_chained(skinny_linear_kernel<MT, WARPS, EPI, OUT>, dim3(tiles),
-                                                     dim3(WARPS * 32), 0, stream, (const __nv_bfloat16*)W,
+    TS_CHAINED_CHECK("skinny_linear", launch_chained(skinny_linear_kernel<MT, WARPS, EPI, OUT, UNROLL, MINB>,
+                                                     dim3(tiles), dim3(WARPS * 32), 0, stream, (const __nv_bfloat16*)W,
                                                      (const __nv_bfloat16*)x, (OUT*)y, M, N, K, ldx, ldy, inter));
     return 0;
 }
 
-template <int WARPS, int EPI, typename OUT>
+template <int WARPS, int EPI, typename OUT, int UNROLL, int MINB>
 int dispatch_m(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
                cudaStream_t stream) {
-    if (M <= 8) return launch<1, WARPS, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
-    if (M <= 16) return launch<2, WARPS, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
-    return launch<4, WARPS, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (M <= 8) return launch<1, WARPS, EPI, OUT, UNROLL, MINB>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (M <= 16) return launch<2, WARPS, EPI, OUT, UNROLL, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    // 32 rows of x with 16 warps: fewer loads in flight, to stay within the 128 registers a thread of 512 can have
+    return launch<4, WARPS, EPI, OUT, (WARPS > 8 ? 2 : UNROLL), 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
 }
 
+int g_warps_override = 0;       // tuning aid: 4, 8 or 16 forces plain 16-row tiles with that many warps; 0: the rules below
+
+// How a product is cut into CTAs, chosen from N and K only (never from the rows of x).  Measured on
+// a B200 with Llama 3.2 1B shapes (16 different weights in a row inside a CUDA graph, so nothing
+// stays in L2): the aim is one wave of CTAs that covers all 148 SMs.
+//   many row tiles (gate/up, vocabulary): 4 warps a tile, 7 CTAs per SM (1,036 slots);
+//   149..296 tiles (q/k/v): 8 warps, 2 CTAs per SM;
+//   up to 148 tiles (output projection, down): 16 warps, one CTA per SM.  (8-row tiles, twice the CTAs,
+//   were no faster: the SMs that get two of them take as long as one 16-row tile.)
 template <int EPI, typename OUT>
 int dispatch_warps(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
                    cudaStream_t stream) {
-    // enough warps in the grid to keep every SM's memory pipes full: 148 SMs x 16 warps
     const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
     const int kblocks = K / 32;
-    int warps = 4;
-    while (warps < 16 && tiles * warps < 148 * 16 && kblocks / (warps * 2) >= 4) warps *= 2;
-    if (warps == 4) return dispatch_m<4, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
-    if (warps == 8) return dispatch_m<8, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
-    return dispatch_m<16, EPI, OUT>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (g_warps_override == 4) return dispatch_m<4, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (g_warps_override == 8) return dispatch_m<8, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (g_warps_override == 16) return dispatch_m<16, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (tiles > 296 || kblocks < 32)
+        return dispatch_m<4, EPI, OUT, 2, 7>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (tiles > 148) return dispatch_m<8, EPI, OUT, 4, 2>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    return dispatch_m<16, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
 }
 
 }  // namespace
 
 TS_API int ts_skinny_linear_max_rows() { return 32; }
+
+TS_API void ts_skinny_linear_force_warps(int warps) { g_warps_override = warps; }
 
 // y[M, N] = x[M, K] . W[N, K]^T (epilogue 0), or y[M, N/2] = swiglu of it with W = [gate rows | up rows]
 // (epilogue 1).  out_dtype: TS_BF16 or TS_F32.
