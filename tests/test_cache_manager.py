@@ -238,3 +238,29 @@ def test_random_orders_of_requests_keep_the_contract(seed, kind):
     check_invariants(m, s)
     assert m.stats().pages_in_use == 0
     assert all(pool.available() == pool.num_pages for pool in m.pools), "a page was lost"
+
+
+def test_a_pending_token_is_amended_before_its_commit_and_dropped_with_a_released_request():
+    from tinyserve_llm_b200.cache.manager import PENDING_TOKEN
+    layout = layout_of(4)
+    storage = FakeStorage(layout, [8])
+    m = CacheManager(layout, 8, storage, caching=True)
+    assert m.admit("a", [1, 2, 3])
+    storage.run_step(m, "a")
+    m.commit("a", 3)
+    m.extend("a", [PENDING_TOKEN])                     # the token is still on the device
+    with pytest.raises(AssertionError, match="pending"):
+        m.commit("a", 1)
+    m.amend_last("a", 9)
+    with pytest.raises(AssertionError, match="no pending token"):
+        m.amend_last("a", 9)
+    storage.run_step(m, "a")
+    m.commit("a", 1)                                   # the page is full: published under its real tokens
+    check_invariants(m, storage)
+    assert m.admission_cost([1, 2, 3, 9, 5]).prefill_tokens == 1
+    m.extend("a", [PENDING_TOKEN])
+    with pytest.raises(AssertionError, match="commit first"):
+        m.release("a")
+    m.release("a", drop_reserved=True)                 # the request ended under a step launched ahead
+    check_invariants(m, storage)
+    assert m.stats().pages_in_use == 0

@@ -61,7 +61,8 @@ def test_greedy_equals_the_plain_implementation_and_reuses_the_shared_prefix(mod
 
 @pytest.mark.parametrize("kwargs", [
     {"caching": False}, {"prefill_chunk": 7, "max_num_batched_tokens": 24}, {"num_blocks": 7, "caching": False},
-    {"step_mode": "prefill_first"}, {"cuda_graphs": False}, {"max_num_seqs": 2}])
+    {"step_mode": "prefill_first"}, {"cuda_graphs": False}, {"max_num_seqs": 2}, {"run_ahead": False},
+    {"run_ahead": False, "cuda_graphs": False}])
 def test_output_does_not_depend_on_how_the_work_is_cut(model_folders, workload_b, kwargs):
     prompts, want = workload_b
     llm = make_llm(model_folders["b"], PAGE_B, **kwargs)
@@ -70,6 +71,10 @@ def test_output_does_not_depend_on_how_the_work_is_cut(model_folders, workload_b
     assert llm.cache.stats().pages_in_use == 0
     if kwargs.get("cuda_graphs", True):
         assert llm.runner.graph_replays > 0, "decode steps were meant to come from CUDA graphs"
+    if kwargs.get("run_ahead", True):
+        assert llm.steps_launched_ahead > 0, "decode steps were meant to be launched ahead of the samples"
+    else:
+        assert llm.steps_launched_ahead == 0
 
 
 @pytest.mark.parametrize("caching", [True, False])
@@ -123,7 +128,7 @@ def test_seeded_sampling_is_reproducible_and_independent_of_the_batch(model_fold
     assert [c.token_ids for c in first] != [c.token_ids for c in other]
     assert all(c.token_ids[0] != c.token_ids[1] for c in first), "the two samples of a request must differ"
     # the same request alone, in portions, without graphs: the same draws (keys are per request and position)
-    alone = make_llm(model_folders["b"], PAGE_B, seed=5, prefill_chunk=16, cuda_graphs=False)
+    alone = make_llm(model_folders["b"], PAGE_B, seed=5, prefill_chunk=16, cuda_graphs=False, run_ahead=False)
     alone.generate([prompts[2]], greedy(1))                         # takes request id 0; ids key the noise
     assert alone.generate([prompts[1]], params)[0].token_ids == first[1].token_ids
 
@@ -140,6 +145,9 @@ def test_eos_stops_generation_and_is_kept(model_folders):
                                            SamplingParams(max_tokens=8, temperature=0.0, ignore_eos=True)])
     assert done[0].token_ids[0] == cut and done[0].finish_reasons == ["eos"]
     assert done[1].token_ids[0] == free and done[1].finish_reasons == ["length"]
+    assert llm.steps_launched_ahead > 0 and llm.cache.stats().pages_in_use == 0
+    alone = llm.generate([prompt], SamplingParams(max_tokens=8, temperature=0.0))[0]    # the step launched behind its end is dropped
+    assert alone.token_ids[0] == cut and llm.cache.stats().pages_in_use == 0 and llm._in_flight is None
     # -1 means: take the model's own end token (the first of config.json's list)
     assert make_llm(model_folders["b"], PAGE_B, eos_token_id=-1).scheduler.config.eos_token_id == 7
 

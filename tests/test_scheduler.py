@@ -12,7 +12,8 @@ import pytest
 from cache_fakes import FakeStorage, check_invariants, layout_of
 from tinyserve_llm_b200.cache import CacheManager
 from tinyserve_llm_b200.engine.scheduler import Scheduler, SchedulerConfig
-from tinyserve_llm_b200.engine.sequence import SamplingParams
+from tinyserve_llm_b200.cache.manager import PENDING_TOKEN
+from tinyserve_llm_b200.engine.sequence import SamplingParams, SequenceStatus
 
 VOCAB = 50
 
@@ -34,36 +35,75 @@ def reference_output(prompt, max_tokens, sample=0, eos=-1):
 
 
 class World:
-    def __init__(self, pages=32, page_tokens=4, caching=True, **config):
+    """
+    Scheduler + cache manager + a fake device.  With `run_ahead` it steps the way the engine does:
+    the step after the one under way is launched first where `schedule_ahead` allows it, its
+    tokens passed on the "device" (the fake computes a launched step at once, the host side sees
+    the samples only when it books the step).
+    """
+
+    def __init__(self, pages=32, page_tokens=4, caching=True, run_ahead=False, eos=None, **config):
         layout = layout_of(page_tokens)
         self.storage = FakeStorage(layout, [pages])
         self.cache = CacheManager(layout, pages, self.storage, caching=caching)
         defaults = dict(max_model_len=64, max_num_seqs=8, max_num_batched_tokens=64, watermark=0.0, prefill_chunk=0)
+        if eos is not None:
+            defaults["eos_token_id"] = eos
         defaults.update(config)
         self.scheduler = Scheduler(SchedulerConfig(**defaults), self.cache)
         self.now = 0.0
         self.batches = []
+        self.run_ahead = run_ahead
+        self.in_flight = None
+        self.launched_ahead = 0
+        self.dropped = 0
 
     def add(self, prompt, **params):
         return self.scheduler.add_request(list(prompt), SamplingParams(**{"temperature": 0.0, **params}), self.now)
 
-    def step(self):
-        batch = self.scheduler.schedule(self.now)
-        assert batch, "empty step"
+    def launch(self, batch, before=None):
+        """Runs the step on the fake device; `before` = (batch, samples) of the step whose samples feed this one."""
         self.batches.append(batch)
+        fed_on_device = {}
+        if before is not None:
+            fed_on_device = {s.seq.seq_id: tokens[0] for s, tokens in zip(*before)}
         sampled = []
+        B = self.cache.page_tokens
         for seq, fed, num_samples in batch:
             state = self.cache.seqs[seq.seq_id]
             assert list(fed) == state.tokens[state.committed:], "fed tokens are not the reserved ones"
-            assert state.tokens == seq.all_token_ids[:state.reserved], "the cache holds other tokens than the sequence"
-            self.storage.run_step(self.cache, seq.seq_id)
-            B = self.cache.page_tokens
+            if before is None:
+                assert state.tokens == seq.all_token_ids[:state.reserved], "the cache holds other tokens than the sequence"
+                self.storage.run_step(self.cache, seq.seq_id)
+            else:
+                assert list(fed) == [PENDING_TOKEN] and state.reserved == state.committed + 1
+                pos = state.committed
+                self.storage.slots[0][state.tables[0][pos // B]][pos % B] = fed_on_device[seq.seq_id]
             history = [self.storage.slots[0][state.tables[0][p // B]][p % B] for p in range(state.reserved)]
-            first = not seq.output_token_ids
+            first = not seq.output_token_ids and before is None
             sampled.append([next_token(history, i if first else 0) for i in range(num_samples)])
+        return batch, sampled
+
+    def step(self):
+        flight, self.in_flight = self.in_flight, None
+        if flight is None:
+            batch = self.scheduler.schedule(self.now)
+            assert batch, "empty step"
+            flight = self.launch(batch)
+        ahead = self.scheduler.schedule_ahead(flight[0]) if self.run_ahead else None
+        following = None
+        if ahead is not None:
+            following = self.launch(ahead, flight)
+            self.launched_ahead += 1
         self.now += 1.0
-        outputs = self.scheduler.postprocess(batch, sampled, self.now)
-        check_invariants(self.cache, self.storage)
+        outputs = self.scheduler.postprocess(flight[0], flight[1], self.now, ahead)
+        if following is not None:
+            if any(s.seq.status is SequenceStatus.RUNNING for s in following[0]):
+                self.in_flight = following
+            else:
+                self.dropped += 1
+        if self.in_flight is None:               # between steps every reserved slot is committed and written
+            check_invariants(self.cache, self.storage)
         return outputs
 
     def run_all(self, limit=2000):
@@ -243,9 +283,11 @@ def test_watermark_holds_pages_back_at_admission_only():
 
 @pytest.mark.parametrize("seed", range(16))
 @pytest.mark.parametrize("caching", [True, False])
-def test_random_workloads_equal_unbatched_generation(seed, caching):
+@pytest.mark.parametrize("run_ahead", [False, True])
+def test_random_workloads_equal_unbatched_generation(seed, caching, run_ahead):
     rng = random.Random(seed * 2 + caching)
-    w = World(pages=rng.choice([12, 20, 40]), page_tokens=rng.choice([2, 4]), caching=caching,
+    eos = rng.choice([None, rng.randrange(VOCAB)])
+    w = World(pages=rng.choice([12, 20, 40]), page_tokens=rng.choice([2, 4]), caching=caching, run_ahead=run_ahead, eos=eos,
               max_num_seqs=rng.choice([3, 6]), max_num_batched_tokens=rng.choice([8, 16, 64]),
               prefill_chunk=rng.choice([0, 3, 7]), step_mode=rng.choice(["mixed", "prefill_first"]),
               max_model_len=40, watermark=rng.choice([0.0, 0.1]))
@@ -259,7 +301,7 @@ def test_random_workloads_equal_unbatched_generation(seed, caching):
                 rid = w.add(prompt, max_tokens=max_tokens, n=n)
             except ValueError:
                 continue
-            expected[rid] = [reference_output(prompt, max_tokens, i) for i in range(n)]
+            expected[rid] = [reference_output(prompt, max_tokens, i, -1 if eos is None else eos) for i in range(n)]
         for _ in range(rng.randrange(1, 4)):
             if w.scheduler.has_unfinished():
                 for out in w.step():
@@ -270,3 +312,81 @@ def test_random_workloads_equal_unbatched_generation(seed, caching):
         got = [s.output_token_ids for s in sorted(done[rid].sequences, key=lambda s: s.sample_index)]
         assert got == want
     assert w.cache.stats().pages_in_use == 0
+
+
+# ---------------------------------------------------------------------- running ahead
+def _outputs(done, rid):
+    return [s.output_token_ids for s in sorted(done[rid].sequences, key=lambda s: s.sample_index)]
+
+
+def test_run_ahead_launches_decode_steps_before_the_samples_are_booked():
+    w = World(run_ahead=True)
+    prompts = [[1, 2, 3, 4, 5], [6, 7, 8]]
+    rids = [w.add(p, max_tokens=9) for p in prompts]
+    done = w.run_all()
+    for rid, p in zip(rids, prompts):
+        assert _outputs(done, rid) == [reference_output(p, 9)]
+    # the prompt step and each decode step but the last had the next step launched behind it
+    assert w.launched_ahead == 8 and w.dropped == 0
+    assert len(w.batches) == 9 and w.cache.stats().pages_in_use == 0
+
+
+def test_run_ahead_needs_an_empty_queue_and_every_running_sequence_in_the_step():
+    w = World(run_ahead=True, max_num_seqs=1)
+    w.add([1, 2, 3], max_tokens=4)
+    w.add([4, 5, 6], max_tokens=4)                 # waits for the sequence cap
+    w.run_all()
+    assert w.launched_ahead == 3                   # only the second request's decodes, once nothing waits
+
+    w = World(run_ahead=True, prefill_chunk=2)
+    w.add([1, 2, 3, 4, 5], max_tokens=3)
+    w.step()
+    assert w.launched_ahead == 0                   # a prompt portion samples nothing: the next step is not a decode
+
+
+def test_run_ahead_leaves_out_a_sequence_that_reaches_max_tokens():
+    w = World(run_ahead=True)
+    a = w.add([1, 2, 3], max_tokens=2)
+    b = w.add([4, 5, 6, 7], max_tokens=5)
+    done = {}
+    done.update({o.request_id: o for o in w.step()})    # prompts; the step launched behind holds both
+    assert [len(x) for x in w.batches] == [2, 2]
+    done.update({o.request_id: o for o in w.step()})    # a's last token is under way: only b goes on
+    assert [s.seq.request_id for s in w.batches[-1]] == [b]
+    done.update(w.run_all())
+    assert _outputs(done, a) == [reference_output([1, 2, 3], 2)] and _outputs(done, b) == [reference_output([4, 5, 6, 7], 5)]
+
+
+def test_run_ahead_changes_nothing_when_pages_are_short():
+    w = World(run_ahead=True, pages=4, page_tokens=4, caching=False)
+    prompts = [[1, 2, 3, 4], [5, 6, 7, 8]]
+    rids = [w.add(p, max_tokens=6) for p in prompts]      # a third page each at position 8; the pool has four
+    done, refused = {}, 0
+    while w.scheduler.has_unfinished():
+        before = w.launched_ahead
+        done.update({o.request_id: o for o in w.step()})
+        if w.launched_ahead == before and len(w.scheduler.running) == 2:
+            refused += 1
+            assert all(s.reserved == s.committed for s in w.cache.seqs.values())
+    assert refused >= 1 and w.scheduler.counters.preemptions >= 1
+    for rid, p in zip(rids, prompts):
+        assert _outputs(done, rid) == [reference_output(p, 6)]
+
+
+def test_end_of_sequence_under_a_step_launched_ahead():
+    prompt = [3, 1, 4, 1, 5]
+    plain = reference_output(prompt, 12)
+    eos = plain[4]                                  # ends the request at its fifth token at the latest
+    want = reference_output(prompt, 12, eos=eos)
+    assert 1 < len(want) < 12
+    w = World(run_ahead=True, eos=eos)
+    other = [2, 7, 1, 8]
+    a, b = w.add(prompt, max_tokens=12), w.add(other, max_tokens=12, ignore_eos=True)
+    done = w.run_all()
+    assert _outputs(done, a) == [want] and _outputs(done, b) == [reference_output(other, 12)]
+    assert w.cache.stats().pages_in_use == 0
+    # alone, the step launched behind its last one is thrown away
+    w = World(run_ahead=True, eos=eos)
+    a = w.add(prompt, max_tokens=12)
+    done = w.run_all()
+    assert _outputs(done, a) == [want] and w.dropped == 1 and w.cache.stats().pages_in_use == 0

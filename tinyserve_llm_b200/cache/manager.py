@@ -105,6 +105,9 @@ class NullStorage:
         pass
 
 
+PENDING_TOKEN = -1      # stands in the token record for a token that is still on the device; amend_last() fills it in
+
+
 @dataclass
 class SeqState:
     tables: list[list[int]]                        # per group, page ids in token order (-1: given back)
@@ -383,6 +386,8 @@ class CacheManager:
         assert 0 <= num_accepted <= seq.reserved - seq.committed, "more slots accepted than reserved"
         assert not self.layout.state_bytes or num_accepted == seq.reserved - seq.committed, \
             "a model with per-request state cannot take back tokens it has run"
+        assert PENDING_TOKEN not in seq.tokens[seq.committed:seq.committed + num_accepted], \
+            "a token still pending would be committed: amend it first"
         B = self.page_tokens
         before = seq.committed
         seq.committed += num_accepted
@@ -433,10 +438,21 @@ class CacheManager:
             table[i] = kept.page
             self._drop(0, page)
 
-    def release(self, seq_id: int) -> None:
-        """Ends a request (finished or preempted).  With prefix reuse its pages stay cached until evicted."""
+    def amend_last(self, seq_id: int, token: int) -> None:
+        """Fills in the one reserved token that was extended as PENDING_TOKEN, before its commit."""
         seq = self.seqs[seq_id]
-        assert seq.reserved == seq.committed, "release between steps: commit first"
+        assert seq.reserved == seq.committed + 1 and seq.tokens[-1] == PENDING_TOKEN, "no pending token to amend"
+        seq.tokens[-1] = token
+
+    def release(self, seq_id: int, drop_reserved: bool = False) -> None:
+        """
+        Ends a request (finished or preempted).  With prefix reuse its pages stay cached until evicted.
+        `drop_reserved`: slots reserved for a step that will not be committed go with it (a request
+        that ended while its next step was already launched).
+        """
+        seq = self.seqs[seq_id]
+        assert drop_reserved or seq.reserved == seq.committed, "release between steps: commit first"
+        del seq.tokens[seq.committed:]
         if self.caching and seq.committed % self.page_tokens:
             self._publish(seq, seq.committed // self.page_tokens)
         del self.seqs[seq_id]

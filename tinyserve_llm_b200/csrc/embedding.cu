@@ -30,3 +30,24 @@ TS_API int ts_embedding(const void* table, const int* ids, void* out, int num_to
         return ts_fail("embedding: unknown dtype code %d", dtype);
     return 0;
 }
+
+// A decode step launched before the host has read the previous step's samples takes its token ids
+// from the sampler's output on the device: an id slot that holds -(j + 2) is replaced by src[j].
+// -1 stays what it is elsewhere (a row that embeds to zeros), and so does an index out of range.
+__global__ void feed_tokens_kernel(int* __restrict__ ids, int n, const int* __restrict__ src, int src_n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int v = ids[i];
+    if (v < -1) {
+        const int j = -v - 2;
+        ids[i] = j < src_n ? src[j] : -1;
+    }
+}
+
+TS_API int ts_feed_tokens(int* ids, int n, const int* src, int src_n, cudaStream_t stream) {
+    TS_REQUIRE(n >= 0 && src_n >= 0, "feed_tokens: bad sizes n=%d src=%d", n, src_n);
+    if (n == 0) return 0;
+    feed_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, n, src, src_n);
+    TS_LAUNCH_CHECK("feed_tokens");
+    return 0;
+}

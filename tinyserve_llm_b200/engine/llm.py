@@ -5,7 +5,8 @@ Names and meanings of the options follow tinyserve-llm (engine/llm_engine.py:66-
 engine/interface.py:28-32): SchedulerConfig, CacheConfig(block_size, caching, device), dtype,
 num_blocks (None: sized from free device memory after a warm-up step), gpu_memory_utilization, seed,
 load_tokenizer; add_request / step / generate; Completion and StepRecord.  There is no `attention`
-option: the engine has one attention implementation, its own kernels.
+option: the engine has one attention implementation, its own kernels.  New here: `cuda_graphs` and
+`run_ahead` (decode steps launched before the previous step's samples have reached the host).
 """
 
 from __future__ import annotations
@@ -21,9 +22,9 @@ from tinyserve_llm_b200.cache.manager import CacheStats, plan_layout
 from tinyserve_llm_b200.cache.storage import DeviceCacheStorage
 from tinyserve_llm_b200.engine.loading import build_cache, load_model, require_cuda, resolve_dtype
 from tinyserve_llm_b200.engine.scheduler import RequestOutput, ScheduledSeq, Scheduler, SchedulerConfig, SchedulerStats
-from tinyserve_llm_b200.engine.sequence import SamplingParams
+from tinyserve_llm_b200.engine.sequence import SamplingParams, SequenceStatus
 from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
-from tinyserve_llm_b200.sampling.sampler import Sampler
+from tinyserve_llm_b200.sampling.sampler import PendingTokens, Sampler
 
 logger = logging.getLogger(__name__)
 
@@ -61,6 +62,15 @@ class Completion:
     finish_time: float
 
 
+@dataclass
+class _InFlight:
+    """A step that has been queued on the device."""
+
+    batch: list[ScheduledSeq]
+    pending: PendingTokens
+    first_draw: dict[int, int]        # sequence id -> index of its first sample among the step's samples
+
+
 class LLM:
     def __init__(
             self,
@@ -75,6 +85,7 @@ class LLM:
             load_tokenizer: bool | None = None,
             random_weights_seed: int | None = None,
             cuda_graphs: bool = True,
+            run_ahead: bool = True,
     ) -> None:
         self.device = require_cuda(cache_config.device)
         self.dtype = resolve_dtype(dtype)
@@ -107,6 +118,9 @@ class LLM:
                                  max_decode_batch=scheduler_config.max_num_seqs)
         self.sampler = Sampler(self.model.rt.ops, self.device, seed)
         self.steps: list[StepRecord] = []
+        self.run_ahead = bool(run_ahead)
+        self._in_flight: _InFlight | None = None
+        self.steps_launched_ahead = 0
         logger.info("cache: %d pages of %d tokens", num_blocks, cache_config.block_size)
 
     # ------------------------------------------------------------------ set-up helpers
@@ -157,34 +171,60 @@ class LLM:
             raise ValueError(f"prompt holds token ids outside the vocabulary of {vocab}")
         return self.scheduler.add_request(token_ids, params, time.perf_counter() if arrival_time is None else arrival_time)
 
-    def _run(self, batch: list[ScheduledSeq]) -> list[list[int]]:
+    def _launch(self, batch: list[ScheduledSeq], before: "_InFlight | None" = None) -> "_InFlight":
+        """
+        Queues the step and its sampling on the device; nothing waits.  With `before` (the step
+        under way, whose samples the host has not seen) every entry's token is that step's sample
+        for the same sequence, passed on the device, and its output position is one further on.
+        """
         entries, temperatures, draws, rows = [], [], [], []
+        first_draw: dict[int, int] = {}
         row = 0
+        lag = 0 if before is None else 1
         for seq, fed, num_samples in batch:
-            entries.append(StepEntry(seq.seq_id, fed, [len(fed) - 1] if num_samples else []))
+            if before is None:
+                entries.append(StepEntry(seq.seq_id, fed, [len(fed) - 1] if num_samples else []))
+            else:
+                entries.append(StepEntry(seq.seq_id, (0,), (0,), feed=before.first_draw[seq.seq_id]))
+            first_draw[seq.seq_id] = len(draws)
             for i in range(num_samples):
                 index = seq.sample_index if num_samples == 1 else i
                 temperatures.append(seq.params.temperature)
-                draws.append((seq.request_id, index, len(seq.output_token_ids)))
+                draws.append((seq.request_id, index, len(seq.output_token_ids) + lag))
                 rows.append(row)
             row += 1 if num_samples else 0
-        logits = self.runner.step(entries)
-        tokens = self.sampler.sample(logits, temperatures, draws, rows)
-        out, i = [], 0
-        for _, _, num_samples in batch:
-            out.append(tokens[i:i + num_samples])
-            i += num_samples
-        return out
+        logits = self.runner.step(entries, None if before is None else before.pending.device_tokens)
+        pending = self.sampler.sample_async(logits, temperatures, draws, rows)
+        return _InFlight(batch, pending, first_draw)
 
     def step(self) -> list[RequestOutput]:
+        """
+        One step's results.  With `run_ahead`, the step after it is launched before this one's
+        samples are read where the scheduler can decide it without them, so the device does not
+        idle while the host books the results; what `step()` returns, and when a request counts
+        as finished, is the same either way.
+        """
         start = time.perf_counter()
-        batch = self.scheduler.schedule(start)
-        if not batch:
-            raise RuntimeError("the scheduler produced an empty step")
-        sampled = self._run(batch)
+        flight = self._in_flight
+        self._in_flight = None
+        if flight is None:
+            batch = self.scheduler.schedule(start)
+            if not batch:
+                raise RuntimeError("the scheduler produced an empty step")
+            flight = self._launch(batch)
+        ahead = self.scheduler.schedule_ahead(flight.batch) if self.run_ahead else None
+        following = self._launch(ahead, flight) if ahead is not None else None
+        self.steps_launched_ahead += ahead is not None
+        tokens = flight.pending.wait()
+        sampled, i = [], 0
+        for _, _, num_samples in flight.batch:
+            sampled.append(tokens[i:i + num_samples])
+            i += num_samples
         end = time.perf_counter()
-        outputs = self.scheduler.postprocess(batch, sampled, end)
-        self.steps.append(StepRecord(start, end, len(batch), sum(len(fed) for _, fed, _ in batch),
+        outputs = self.scheduler.postprocess(flight.batch, sampled, end, ahead)
+        if following is not None and any(s.seq.status is SequenceStatus.RUNNING for s in following.batch):
+            self._in_flight = following          # else every sequence in it has finished: its results are dropped
+        self.steps.append(StepRecord(start, end, len(flight.batch), sum(len(fed) for _, fed, _ in flight.batch),
                                      self.scheduler.stats(), self.cache.stats()))
         return outputs
 

@@ -19,6 +19,14 @@ cached for reuse), it returns to the waiting queue with its outputs and arrival 
 run again from its whole token list.  A prompt portion that finds no page waits for a later step.
 If a step would otherwise be empty while sequences are running, the lowest-scoring one is preempted
 and the step is built again; a step that is empty with nothing running raises in the engine.
+
+Running ahead (new here).  While a decode step is still on the device, `schedule_ahead` may decide
+the step after it: every running sequence feeds the token it is about to sample, which the engine
+passes from step to step on the device.  It does so only where the decision does not depend on
+those tokens: nothing waits, everything running is in the step and samples one token, and the pages
+for one more token each are free.  A sequence that reaches `max_tokens` in the step under way is
+left out.  The one thing unknown is an end-of-sequence token: a sequence that samples one finishes
+as usual, its pages are released, and its share of the step launched ahead is thrown away.
 """
 
 from __future__ import annotations
@@ -28,7 +36,7 @@ import math
 from dataclasses import dataclass, replace
 from typing import NamedTuple
 
-from tinyserve_llm_b200.cache.manager import AdmissionCost, CacheManager
+from tinyserve_llm_b200.cache.manager import PENDING_TOKEN, AdmissionCost, CacheManager
 from tinyserve_llm_b200.engine.sequence import SamplingParams, Sequence, SequenceStatus
 
 
@@ -282,6 +290,38 @@ class Scheduler:
             self.waiting = [s for s in self.waiting if s.seq_id not in chosen]
         return admitted
 
+    # ------------------------------------------------------------------ the step after the one under way
+    def schedule_ahead(self, under_way: list[ScheduledSeq]) -> list[ScheduledSeq] | None:
+        """
+        The step that follows `under_way`, whose samples are not known yet; None where that step
+        depends on them (then nothing is changed).  Otherwise `under_way` is committed here (its
+        tokens are known, and whatever reads their keys is launched after it), each continuing
+        sequence reserves one slot with PENDING_TOKEN as its token, and `postprocess` is told so.
+        """
+        if self.waiting:
+            return None
+        alive = [s for s in under_way if s.seq.status is SequenceStatus.RUNNING]
+        if any(s.num_samples != 1 for s in alive) or {s.seq.seq_id for s in alive} != {s.seq_id for s in self.running}:
+            return None
+        # the step under way produces output number len(outputs) + 1
+        going_on = [s.seq for s in alive if len(s.seq.output_token_ids) + 1 < s.seq.params.max_tokens]
+        if not going_on:
+            return None
+        needed = [0] * len(self.cache.pools)
+        for seq in going_on:
+            for g, pages in enumerate(self.cache.pages_needed_to_extend(seq.seq_id, 1)):
+                needed[g] += pages
+        if not self.cache.fits(needed):
+            return None                          # someone has to give way: decided when the tokens are known
+        for s in alive:
+            self.cache.commit(s.seq.seq_id, len(s.token_ids))
+        ahead = []
+        for seq in going_on:
+            self.cache.extend(seq.seq_id, [PENDING_TOKEN])
+            ahead.append(ScheduledSeq(seq, [PENDING_TOKEN], 1))
+            self.counters.decode_tokens += 1
+        return ahead
+
     # ------------------------------------------------------------------ after the model ran
     def _fork(self, parent: Sequence, index: int) -> Sequence:
         child = Sequence(next(self._seq_ids), parent.request_id, parent.prompt_token_ids, parent.params,
@@ -299,12 +339,24 @@ class Scheduler:
             return "length"
         return None
 
-    def postprocess(self, scheduled: list[ScheduledSeq], sampled: list[list[int]], now: float) -> list[RequestOutput]:
-        """Commits the step, forks groups after their first sampling step, records tokens, frees what finished."""
+    def postprocess(self, scheduled: list[ScheduledSeq], sampled: list[list[int]], now: float,
+                    ahead: list[ScheduledSeq] | None = None) -> list[RequestOutput]:
+        """
+        Commits the step, forks groups after their first sampling step, records tokens, frees what
+        finished.  `ahead` is what `schedule_ahead(scheduled)` returned: the step is committed
+        already, and the sequences in `ahead` get their pending token filled in.  Samples of a
+        sequence that finished while this step was launched ahead are dropped.
+        """
         finished: list[Sequence] = []
+        pending = {s.seq.seq_id for s in ahead} if ahead is not None else ()
         for (seq, token_ids, num_samples), tokens in zip(scheduled, sampled, strict=True):
             assert len(tokens) == num_samples
-            self.cache.commit(seq.seq_id, len(token_ids))
+            if seq.status is SequenceStatus.FINISHED:
+                continue
+            if ahead is None:
+                self.cache.commit(seq.seq_id, len(token_ids))
+            elif seq.seq_id in pending:
+                self.cache.amend_last(seq.seq_id, tokens[0])
             if num_samples == 0:
                 continue
             samples = [seq] + [self._fork(seq, i) for i in range(1, num_samples)]
@@ -314,7 +366,7 @@ class Scheduler:
                     sample.first_token_time = now
                 reason = self._finish_reason(sample, token)
                 if reason is not None:
-                    self.cache.release(sample.seq_id)
+                    self.cache.release(sample.seq_id, drop_reserved=sample.seq_id in pending)
                     sample.status = SequenceStatus.FINISHED
                     sample.finish_reason = reason
                     sample.finish_time = now

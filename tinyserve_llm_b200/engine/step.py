@@ -32,6 +32,7 @@ class StepEntry:
     seq_id: int
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)    # indices into `tokens`
+    feed: int = -1      # >= 0: the entry's one token is element `feed` of the step's `device_tokens`; `tokens` is a placeholder
 
 
 @dataclass
@@ -120,7 +121,7 @@ class StepRunner:
         self.graph_replays = 0
 
     # ------------------------------------------------------------------ packing
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> None:
         if not entries:
             raise ValueError("a step needs at least one entry")
         vocab, max_pos = self.model.spec.vocab_size, self.model.spec.max_positions
@@ -141,7 +142,13 @@ class StepRunner:
             if state.committed + n > max_pos:
                 raise ValueError(f"request {e.seq_id!r} would reach position {state.committed + n - 1}; "
                                  f"the model's position table has {max_pos}")
-            lo, hi = min(e.tokens), max(e.tokens)
+            if e.feed >= 0:
+                if n != 1 or device_tokens is None or e.feed >= device_tokens.shape[0]:
+                    raise ValueError(f"request {e.seq_id!r}: a token fed on the device is one token, element "
+                                     f"{e.feed} of a `device_tokens` tensor that holds it")
+                lo = hi = 0
+            else:
+                lo, hi = min(e.tokens), max(e.tokens)
             if lo < 0 or hi >= vocab:
                 raise ValueError(f"request {e.seq_id!r}: token id {lo if lo < 0 else hi} outside the vocabulary of {vocab}")
             for w in e.want:
@@ -164,7 +171,7 @@ class StepRunner:
             state = mgr.seqs[e.seq_id]
             n = len(e.tokens)
             first = state.committed
-            ids.extend(e.tokens)
+            ids.extend(e.tokens if e.feed < 0 else (-(e.feed + 2),))
             positions.extend(range(first, first + n))
             seq_of_token.extend([s] * n)
             rows.extend(cu_q[-1] + w for w in e.want)
@@ -234,13 +241,21 @@ class StepRunner:
 
     # ------------------------------------------------------------------ the step
     @torch.inference_mode()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """float32 [wanted places, vocab] on the device, in the order of the entries and of their `want`."""
-        self._validate(entries)
+    def step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
+        """
+        float32 [wanted places, vocab] on the device, in the order of the entries and of their `want`.
+
+        `device_tokens` (int32, on the device) serves entries with `feed` >= 0: their token is read
+        from it on the device, so a decode step can be launched before the host has seen the
+        previous step's samples.
+        """
+        self._validate(entries, device_tokens)
         self.model.rt.ops.check_device_errors()      # a bounded wait that ran out in an earlier step (host-visible word)
         if self.cuda_graphs and len(entries) <= self.max_decode_batch and all(len(e.tokens) == 1 for e in entries):
-            return self._decode_step(entries)
+            return self._decode_step(entries, device_tokens)
         ctx = self._pack(entries)
+        if device_tokens is not None:
+            self.model.rt.ops.feed_tokens(ctx.token_ids, device_tokens)
         x, residual = self.model.forward(ctx)
         if ctx.rows.numel() == 0:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
@@ -254,13 +269,15 @@ class StepRunner:
             b *= 2
         return b
 
-    def _decode_step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _decode_step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         size = self.bucket(len(entries))
         captured = self._graphs.get(size)
         if captured is None:
-            captured = self._capture(entries, size)
+            captured = self._capture(entries, size, device_tokens)
         else:
             self._refill(entries, size, captured)
+            if device_tokens is not None:
+                self.model.rt.ops.feed_tokens(captured.index_buffer[:size], device_tokens)
             captured.graph.replay()
             self.model.rt.ops.launches += captured.launches
         self.graph_replays += 1
@@ -288,7 +305,7 @@ class StepRunner:
             if pad:
                 packed.extend([0] * pad)
 
-        section([e.tokens[0] for e in entries] + [0] * extra)                    # token ids
+        section([e.tokens[0] if e.feed < 0 else -(e.feed + 2) for e in entries] + [0] * extra)    # token ids
         section(first + [0] * extra)                                              # positions
         section(list(range(n)) + [-1] * extra)                                    # request of each token
         section(list(range(size + 1)))                                            # offsets: one token each
@@ -315,11 +332,13 @@ class StepRunner:
         captured.index_buffer[:total].copy_(self._staging[:total], non_blocking=True)
         self._staged.record()
 
-    def _capture(self, entries: Sequence[StepEntry], size: int) -> _DecodeGraph:
+    def _capture(self, entries: Sequence[StepEntry], size: int, device_tokens: torch.Tensor | None = None) -> _DecodeGraph:
         widths = list(self._graph_widths)
         probe = self._pack(entries, pad_to=size, widths=widths)
         index_buffer = torch.empty(probe.index_words, dtype=torch.int32, device=self.device)
         ctx = self._pack(entries, pad_to=size, widths=widths, into=index_buffer)
+        if device_tokens is not None:
+            self.model.rt.ops.feed_tokens(ctx.token_ids, device_tokens)
         # once eagerly: libraries create their handles and workspaces outside the capture; the
         # step's keys and values are written by this run and again, identically, by the replay
         x, residual = self.model.forward(ctx)

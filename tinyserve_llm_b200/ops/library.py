@@ -82,6 +82,12 @@ class Ops:
                    c_int(table.shape[0]), c_int(_DTYPE_CODE[table.dtype]), _stream())
         return out
 
+    def feed_tokens(self, ids: torch.Tensor, source: torch.Tensor) -> None:
+        """In place: an id slot that holds -(j + 2) becomes source[j] (the previous step's sample j, still on the device)."""
+        self._check(ids, "token ids", torch.int32, 1)
+        self._check(source, "sampled tokens", torch.int32, 1)
+        self._call("ts_feed_tokens", _ptr(ids), c_int(ids.shape[0]), _ptr(source), c_int(source.shape[0]), _stream())
+
     def add_rmsnorm(self, x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, eps: float,
                     rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         """
