@@ -303,21 +303,25 @@ template <int HD>
 __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
-    chain_wait();                                              // the step's key and query come from the kernel before
-    chain_release();
+    // Before the wait for the kernel ahead on the stream: what does not depend on it.  The index
+    // data was written by the host before the step, and the keys and values of earlier steps lie
+    // in the pages already; the kernel ahead (rotary + store) writes this step's query and the
+    // one new key and value, so only the tile that holds position ctx - 1 is read after the wait.
     const int q_begin = p.cu_q[seq];
-    if (p.cu_q[seq + 1] - q_begin != 1) return;
+    const bool decoding = p.cu_q[seq + 1] - q_begin == 1;
     const int ctx = p.ctx_lens[seq];
     const int pos = ctx - 1;
     const int g = p.nh / p.nkv;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int key_begin = split * SPLIT;
-    const bool active = key_begin <= pos && key_begin + SPLIT > first_key;
+    const bool active = decoding && key_begin <= pos && key_begin + SPLIT > first_key;
     float* part_o = p.partial_o + (((long long)seq * p.nh + kvh * g) * p.max_splits + split) * HD;
     float* part_ml = p.partial_ml + (((long long)seq * p.nh + kvh * g) * p.max_splits + split) * 2;
     if (!active) {
-        if (split < p.max_splits && tid < g) {                 // an empty split: the combine skips it
+        chain_wait();
+        chain_release();
+        if (decoding && split < p.max_splits && tid < g) {     // an empty split: the combine skips it
             part_ml[(long long)tid * p.max_splits * 2] = -INFINITY;
             part_ml[(long long)tid * p.max_splits * 2 + 1] = 0.f;
         }
@@ -331,16 +335,29 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
     const int* table = p.block_table + (long long)seq * p.table_width;
     const int key0 = key_begin + warp * TILE;
     const bool warp_active = key0 <= pos && key0 + TILE > first_key;
+    const bool holds_new = warp_active && key0 + TILE > pos;
+    const __nv_bfloat16 *k_src = nullptr, *v_src = nullptr;
+    int valid = 0;
+    if (warp_active) {
+        k_src = kv_row<HD>(p.k_pool, p.geo, table, kvh, key0);
+        v_src = kv_row<HD>(p.v_pool, p.geo, table, kvh, key0);
+        valid = k_src ? min(TILE, ctx - key0) : 0;
+        if (!holds_new) {
+            load_tile<HD>(k_tile, k_src ? k_src : p.k_pool, HD, TILE, valid, lane, 32);
+            load_tile<HD>(v_tile, v_src ? v_src : p.v_pool, HD, TILE, valid, lane, 32);
+            cp_async_commit();
+        }
+    }
+    chain_wait();
+    chain_release();
     RowState<HD> st;
     if (warp_active) {
         // rows 0..g-1 of the query tile are the g heads of this kv head; the rest are zero
         load_tile<HD>(q_tile, p.qkv + (long long)q_begin * row_width + (long long)kvh * g * HD, HD, 16, g, lane, 32);
-        const __nv_bfloat16* k_src = kv_row<HD>(p.k_pool, p.geo, table, kvh, key0);
-        const __nv_bfloat16* v_src = kv_row<HD>(p.v_pool, p.geo, table, kvh, key0);
-        const int valid = k_src ? min(TILE, ctx - key0) : 0;
-        load_tile<HD>(k_tile, k_src ? k_src : p.k_pool, HD, TILE, valid, lane, 32);
-        cp_async_commit();
-        load_tile<HD>(v_tile, v_src ? v_src : p.v_pool, HD, TILE, valid, lane, 32);
+        if (holds_new) {
+            load_tile<HD>(k_tile, k_src ? k_src : p.k_pool, HD, TILE, valid, lane, 32);
+            load_tile<HD>(v_tile, v_src ? v_src : p.v_pool, HD, TILE, valid, lane, 32);
+        }
         cp_async_commit();
         cp_async_wait<0>();
         __syncwarp();
@@ -399,28 +416,52 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
     }
 }
 
-// One block per (request, head): merges the splits in order and writes the output row.
+// One block per (request, head): merges the splits in order and writes the output row.  The loads
+// of a chunk of splits are all issued before any is used, so that the kernel pays a memory latency
+// or two, not one per split.
 template <int HD>
 __global__ void decode_combine_kernel(AttnParams p) {
     const int seq = blockIdx.y, head = blockIdx.x;
+    const int q_begin = p.cu_q[seq];              // index data: written by the host before the step
+    const int q_len = p.cu_q[seq + 1] - q_begin;
+    const int ctx = p.ctx_lens[seq];
     chain_wait();
     chain_release();
-    const int q_begin = p.cu_q[seq];
-    if (p.cu_q[seq + 1] - q_begin != 1) return;
-    const int ctx = p.ctx_lens[seq];
+    if (q_len != 1) return;
     const int splits = (ctx + SPLIT - 1) / SPLIT;
     const float* part_o = p.partial_o + ((long long)seq * p.nh + head) * p.max_splits * HD;
-    const float* part_ml = p.partial_ml + ((long long)seq * p.nh + head) * p.max_splits * 2;
-    float m = -INFINITY;
-    for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[2 * s]);
+    const float2* part_ml = reinterpret_cast<const float2*>(p.partial_ml) + ((long long)seq * p.nh + head) * p.max_splits;
     const int d = threadIdx.x;
+    constexpr int CH = 16;
+    float2 ml[CH];
+    float ov[CH];
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+        const bool ok = j < splits;
+        ml[j] = ok ? part_ml[j] : make_float2(-INFINITY, 0.f);
+        ov[j] = ok ? part_o[(long long)j * HD + d] : 0.f;
+    }
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < CH; ++j) m = fmaxf(m, ml[j].x);
+    for (int s = CH; s < splits; ++s) m = fmaxf(m, part_ml[s].x);
     float l = 0.f, o = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[2 * s];
-        if (ms == -INFINITY) continue;
-        const float f = exp2f(ms - m);
-        l += part_ml[2 * s + 1] * f;
-        o += part_o[(long long)s * HD + d] * f;
+    for (int s0 = 0; s0 < splits; s0 += CH) {
+        if (s0 > 0) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+                const bool ok = s0 + j < splits;
+                ml[j] = ok ? part_ml[s0 + j] : make_float2(-INFINITY, 0.f);
+                ov[j] = ok ? part_o[(long long)(s0 + j) * HD + d] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+            if (ml[j].x == -INFINITY) continue;           // an empty split (its partial output was never written)
+            const float f = exp2f(ml[j].x - m);
+            l += ml[j].y * f;
+            o += ov[j] * f;
+        }
     }
     p.out[((long long)q_begin * p.nh + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
 }

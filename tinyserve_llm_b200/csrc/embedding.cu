@@ -11,6 +11,12 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
     const bool valid = id >= 0 && id < vocab;      // padding rows carry id -1: they get zeros
     const T* src = table + (long long)(valid ? id : 0) * hidden;
     T* dst = out + (long long)t * hidden;
+    constexpr int VN = 16 / sizeof(T);
+    if (hidden % VN == 0 && (uintptr_t)table % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        for (int i = threadIdx.x * VN; i < hidden; i += blockDim.x * VN)
+            *reinterpret_cast<uint4*>(dst + i) = valid ? *reinterpret_cast<const uint4*>(src + i) : make_uint4(0, 0, 0, 0);
+        return;
+    }
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = valid ? src[i] : from_float<T>(0.f);
 }
 

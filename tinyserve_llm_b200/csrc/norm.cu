@@ -15,6 +15,15 @@ __global__ void add_rmsnorm_kernel(const T* x, const T* residual, const W* __res
     extern __shared__ float sums[];              // hidden floats: the unrounded sum, then 33 of scratch
     float* scratch = sums + hidden;
     const int r = blockIdx.x;
+    constexpr int VN = VecOf<T>::N;
+    // the weights do not depend on the kernel ahead on the stream: the thread's first chunk is asked
+    // for before the wait for that kernel
+    float wv[VN];
+    const int i0 = threadIdx.x * VN;
+    if (VECTOR && i0 < hidden) {
+#pragma unroll
+        for (int e = 0; e < VN; ++e) wv[e] = to_float<W>(weight[i0 + e]);
+    }
     chain_wait();
     chain_release();
     const int src = rows ? rows[r] : r;
@@ -22,7 +31,6 @@ __global__ void add_rmsnorm_kernel(const T* x, const T* residual, const W* __res
     const T* xr = x + (long long)src * hidden;
     const T* rr = residual ? residual + (long long)src * hidden : nullptr;
     float acc = 0.f;
-    constexpr int VN = VecOf<T>::N;
     if (VECTOR) {                                  // hidden is a multiple of VN and the rows are 16-byte aligned
         for (int i = threadIdx.x * VN; i < hidden; i += blockDim.x * VN) {
             const uint4 xv = *reinterpret_cast<const uint4*>(xr + i);
@@ -59,7 +67,8 @@ __global__ void add_rmsnorm_kernel(const T* x, const T* residual, const W* __res
             for (int e = 0; e < VN; ++e) {
                 const float s = sums[i + e];
                 re[e] = from_float<T>(s);
-                oe[e] = from_float<T>(round_to<T>(s * inv) * to_float<W>(weight[i + e]));
+                const float w = i == i0 ? wv[e] : to_float<W>(weight[i + e]);
+                oe[e] = from_float<T>(round_to<T>(s * inv) * w);
             }
             if (resr) *reinterpret_cast<uint4*>(resr + i) = rv;
             *reinterpret_cast<uint4*>(outr + i) = ov;

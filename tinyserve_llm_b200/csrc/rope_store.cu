@@ -72,10 +72,14 @@ __global__ void rope_store_vec_kernel(T* qkv, const int* __restrict__ positions,
                                       int table_width, T* k_pool, T* v_pool, KVGeometry geo, int nh, int nkv, int hd,
                                       int write_kv) {
     const int t = blockIdx.x;
-    chain_wait();
-    chain_release();
+    // Before the wait for the kernel ahead on the stream (the q/k/v projection): the index data,
+    // which the host wrote before the step, and the angles of the thread's first chunk.
     const int seq = seq_of_token[t];
-    if (seq < 0) return;
+    if (seq < 0) {
+        chain_wait();
+        chain_release();
+        return;
+    }
     const int pos = positions[t];
     const int row_width = (nh + 2 * nkv) * hd;
     T* row = qkv + (long long)t * row_width;
@@ -90,7 +94,25 @@ __global__ void rope_store_vec_kernel(T* qkv, const int* __restrict__ positions,
     const long long head_stride = (long long)geo.page_tokens * hd;
     const int pair_chunks = half / VN, pass_chunks = (hd - rot) / VN;
     const int per_head = pair_chunks + pass_chunks;
-    for (int w = threadIdx.x; w < (nh + nkv) * per_head; w += blockDim.x) {
+    const int total = (nh + nkv) * per_head;
+    float c[VN], sn[VN];
+    auto load_angles = [&](int i) {
+#pragma unroll
+        for (int e = 0; e < VN; e += 4) {
+            const float4 cv = *reinterpret_cast<const float4*>(cs + i + e);
+            const float4 sv = *reinterpret_cast<const float4*>(cs + half + i + e);
+            c[e] = cv.x, c[e + 1] = cv.y, c[e + 2] = cv.z, c[e + 3] = cv.w;
+            sn[e] = sv.x, sn[e + 1] = sv.y, sn[e + 2] = sv.z, sn[e + 3] = sv.w;
+        }
+    };
+    bool have_angles = false;
+    if (cs && (int)threadIdx.x < total && (int)threadIdx.x % per_head < pair_chunks) {
+        load_angles(((int)threadIdx.x % per_head) * VN);
+        have_angles = true;
+    }
+    chain_wait();
+    chain_release();
+    for (int w = threadIdx.x; w < total; w += blockDim.x) {
         const int head = w / per_head, ch = w % per_head;
         T* h = row + (long long)head * hd;
         const bool is_k = head >= nh;
@@ -98,6 +120,8 @@ __global__ void rope_store_vec_kernel(T* qkv, const int* __restrict__ positions,
         if (ch < pair_chunks) {
             const int i = ch * VN;
             uint4 a = *reinterpret_cast<const uint4*>(h + i), b = *reinterpret_cast<const uint4*>(h + i + half), oa, ob;
+            if (cs && !have_angles) load_angles(i);
+            have_angles = false;
             const T* ae = reinterpret_cast<const T*>(&a);
             const T* be = reinterpret_cast<const T*>(&b);
             T* oae = reinterpret_cast<T*>(&oa);
@@ -107,9 +131,8 @@ __global__ void rope_store_vec_kernel(T* qkv, const int* __restrict__ positions,
                 const float x1 = to_float<T>(ae[e]), x2 = to_float<T>(be[e]);
                 float y1 = x1, y2 = x2;
                 if (cs) {
-                    const float c = cs[i + e], sn = cs[half + i + e];
-                    y1 = x1 * c - x2 * sn;
-                    y2 = x2 * c + x1 * sn;
+                    y1 = x1 * c[e] - x2 * sn[e];
+                    y2 = x2 * c[e] + x1 * sn[e];
                 }
                 oae[e] = from_float<T>(y1);
                 obe[e] = from_float<T>(y2);
@@ -152,7 +175,7 @@ TS_API int ts_rope_store(void* qkv, const int* positions, const int* seq_of_toke
     const int threads = 256;
     const int vn = dtype == TS_F32 ? 4 : 8;
     const bool aligned = (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0 &&
-                         page_stride % vn == 0 && entry_offset % vn == 0;
+                         page_stride % vn == 0 && entry_offset % vn == 0 && (uintptr_t)table % 16 == 0;
     if ((dtype == TS_F32 || dtype == TS_BF16) && aligned && hd % vn == 0 && (rot / 2) % vn == 0) {
         const int work = (nh + nkv) * ((rot / 2 + hd - rot) / vn);
         const int vthreads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
