@@ -10,7 +10,11 @@
 //    one tile; the keys are cut into splits of 256 (fixed by key index, so the sums do not depend on
 //    the batch); a CTA takes one split, each of its warps one tile of 64 keys; warps merge in
 //    shared memory and write (max, sum, output) partials to scratch; a second kernel combines the
-//    splits of each head.
+//    splits of each head.  The kernel is bound by the length of a warp's instruction stream, not by
+//    the tensor pipe or by memory: tiles are loaded with folded addresses, tiles that are wholly
+//    visible skip the mask, the padding rows of the tile skip the softmax, the fresh state skips the
+//    rescale, and what does not depend on the kernel ahead on the stream is read before the wait
+//    for it.
 //
 // Keys and values beyond the request's length (the unwritten tail of its last page) are zero-filled
 // on load and masked by select, so whatever those slots hold never reaches a result.
@@ -22,8 +26,13 @@ constexpr int TILE = 64;           // keys per tile, queries per prefill CTA
 #ifndef TS_DECODE_WARPS
 #define TS_DECODE_WARPS 4
 #endif
-constexpr int DW = TS_DECODE_WARPS;  // warps of a decode CTA, one tile of 64 keys each
-constexpr int SPLIT = DW * TILE;    // keys per decode split
+#ifndef TS_DECODE_TILE
+#define TS_DECODE_TILE 64
+#endif
+constexpr int DW = TS_DECODE_WARPS;  // warps of a decode CTA, one tile of DKT keys each
+constexpr int DKT = TS_DECODE_TILE;  // keys per warp of a decode CTA: small tiles, many warps, to hide the tile routine's latencies
+constexpr int SPLIT = DW * DKT;     // keys per decode split
+static_assert(DKT % 16 == 0 && TILE % DKT == 0, "a decode tile is a multiple of 16 keys and divides a prefill tile (and so a page)");
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -79,6 +88,25 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat
     }
 }
 
+// One warp loads a tile whose ROWS rows lie back to back in memory (a head's keys of one page).
+// Lane l takes 16-byte chunk l % CHUNKS of rows l / CHUNKS + j * (32 / CHUNKS): the row is
+// r0 | const_j, so its swizzle is (chunk ^ r0) ^ const_j and every address is one base plus constants.
+template <int HD, int ROWS, bool FULL>
+__device__ __forceinline__ void load_tile_warp(__nv_bfloat16* tile, const __nv_bfloat16* src, int valid_rows, int lane) {
+    constexpr int CHUNKS = HD / 8, RPI = 32 / CHUNKS;      // rows per iteration: 4 (head 64) or 2 (head 128)
+    static_assert(ROWS % RPI == 0 && RPI <= 8, "tile rows must be a multiple of the rows one pass covers");
+    const int c = lane % CHUNKS, r0 = lane / CHUNKS;
+    const uint32_t base = smem_u32(tile) + r0 * HD * 2;
+    const uint32_t swz = (uint32_t)(c ^ r0) << 4;
+    const __nv_bfloat16* g = src + lane * 8;
+#pragma unroll
+    for (int j = 0; j < ROWS / RPI; ++j) {
+        const uint32_t dst = base + j * RPI * HD * 2 + (swz ^ (((j * RPI) & 7) << 4));
+        const int bytes = (FULL || r0 + j * RPI < valid_rows) ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(FULL || bytes ? g + j * RPI * HD : src), "r"(bytes));
+    }
+}
+
 // Running softmax state of the two rows a thread owns (lane/4 and lane/4 + 8 of the warp's 16).
 template <int HD>
 struct RowState {
@@ -93,23 +121,26 @@ struct RowState {
     }
 };
 
-// One tile of 64 keys against the warp's 16 query rows.  q: the rows' A fragments; k_tile/v_tile:
+// One tile of KT keys against the warp's 16 query rows.  q: the rows' A fragments; k_tile/v_tile:
 // swizzled [64][HD]; key0: index of the tile's first key; pos[2]: positions of the thread's two rows
 // (keys lo[i]..pos[i] are visible).
-template <int HD, bool MASK>
+// FIRST: the state is fresh (no key seen yet), so there is nothing to rescale.  TOP: only rows 0..7 of
+// the tile are real (a decode group of at most 8 heads); the softmax of rows 8..15 is skipped, their
+// probabilities are zero.
+template <int HD, bool MASK, int KT = TILE, bool FIRST = false, bool TOP = false>
 __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q)[HD / 16][4], __nv_bfloat16* k_tile,
                                             __nv_bfloat16* v_tile, int key0, const int (&pos)[2], const int (&lo)[2],
                                             float scale_log2, int lane) {
-    float s[TILE / 8][4];
+    float s[KT / 8][4];
 #pragma unroll
-    for (int n = 0; n < TILE / 8; ++n)
+    for (int n = 0; n < KT / 8; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
     // S = Q K^T
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk) {
 #pragma unroll
-        for (int nb = 0; nb < TILE / 16; ++nb) {
+        for (int nb = 0; nb < KT / 16; ++nb) {
             uint32_t b[4];
             const int row = nb * 16 + (lane & 7) + ((lane >> 4) << 3);
             const int chunk = kk * 2 + ((lane >> 3) & 1);
@@ -121,9 +152,9 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
     // mask, running maximum (of raw scores; the scale is positive and joins the exponent below)
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int n = 0; n < TILE / 8; ++n) {
+    for (int n = 0; n < KT / 8; ++n) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < (TOP ? 2 : 4); ++e) {
             const int r = e >> 1;
             if (MASK) {                                   // tiles wholly inside every row's range skip the test
                 const int key = key0 + n * 8 + ((lane & 3) << 1) + (e & 1);
@@ -132,9 +163,9 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
             tile_max[r] = fmaxf(tile_max[r], s[n][e]);
         }
     }
-    float corr[2], m_use[2];
+    float corr[2] = {1.f, 1.f}, m_use[2] = {0.f, 0.f};
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < (TOP ? 1 : 2); ++r) {
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
         tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
         const float m_new = fmaxf(st.m[r], tile_max[r] * scale_log2);   // -inf stays -inf
@@ -143,17 +174,23 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
         st.m[r] = m_new;
         st.l[r] *= corr[r];
     }
+    if (!FIRST) {
 #pragma unroll
-    for (int n = 0; n < HD / 8; ++n) {
-        st.o[n][0] *= corr[0]; st.o[n][1] *= corr[0];
-        st.o[n][2] *= corr[1]; st.o[n][3] *= corr[1];
+        for (int n = 0; n < HD / 8; ++n) {
+            st.o[n][0] *= corr[0]; st.o[n][1] *= corr[0];
+            st.o[n][2] *= corr[1]; st.o[n][3] *= corr[1];
+        }
     }
     // P = exp2(S - m), sums in float32, P rounded to bfloat16 for the second product
-    uint32_t p[TILE / 16][4];
+    uint32_t p[KT / 16][4];
 #pragma unroll
-    for (int n = 0; n < TILE / 8; ++n) {
+    for (int n = 0; n < KT / 8; ++n) {
         const float p0 = fast_exp2(fmaf(s[n][0], scale_log2, -m_use[0])), p1 = fast_exp2(fmaf(s[n][1], scale_log2, -m_use[0]));
-        const float p2 = fast_exp2(fmaf(s[n][2], scale_log2, -m_use[1])), p3 = fast_exp2(fmaf(s[n][3], scale_log2, -m_use[1]));
+        float p2 = 0.f, p3 = 0.f;
+        if (!TOP) {
+            p2 = fast_exp2(fmaf(s[n][2], scale_log2, -m_use[1]));
+            p3 = fast_exp2(fmaf(s[n][3], scale_log2, -m_use[1]));
+        }
         st.l[0] += p0 + p1;
         st.l[1] += p2 + p3;
         p[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
@@ -161,7 +198,7 @@ __device__ __forceinline__ void attend_tile(RowState<HD>& st, const uint32_t (&q
     }
     // O += P V
 #pragma unroll
-    for (int kk = 0; kk < TILE / 16; ++kk) {
+    for (int kk = 0; kk < KT / 16; ++kk) {
 #pragma unroll
         for (int nb = 0; nb < HD / 16; ++nb) {
             uint32_t b[4];
@@ -327,40 +364,45 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
         }
         return;
     }
-    // shared memory: per warp a query tile [16][HD], a key tile and a value tile [64][HD]
-    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw) + warp * (16 + 2 * TILE) * HD;
-    __nv_bfloat16* k_tile = q_tile + 16 * HD;
-    __nv_bfloat16* v_tile = k_tile + TILE * HD;
+    // shared memory: one query tile [16][HD], then per warp a key tile and a value tile [DKT][HD]
+    __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* k_tile = q_tile + 16 * HD + warp * 2 * DKT * HD;
+    __nv_bfloat16* v_tile = k_tile + DKT * HD;
     const int row_width = (p.nh + 2 * p.nkv) * HD;
     const int* table = p.block_table + (long long)seq * p.table_width;
-    const int key0 = key_begin + warp * TILE;
-    const bool warp_active = key0 <= pos && key0 + TILE > first_key;
-    const bool holds_new = warp_active && key0 + TILE > pos;
+    const int key0 = key_begin + warp * DKT;
+    const bool warp_active = key0 <= pos && key0 + DKT > first_key;
+    const bool holds_new = warp_active && key0 + DKT > pos;
     const __nv_bfloat16 *k_src = nullptr, *v_src = nullptr;
     int valid = 0;
     if (warp_active) {
         k_src = kv_row<HD>(p.k_pool, p.geo, table, kvh, key0);
         v_src = kv_row<HD>(p.v_pool, p.geo, table, kvh, key0);
-        valid = k_src ? min(TILE, ctx - key0) : 0;
+        valid = k_src ? min(DKT, ctx - key0) : 0;
         if (!holds_new) {
-            load_tile<HD>(k_tile, k_src ? k_src : p.k_pool, HD, TILE, valid, lane, 32);
-            load_tile<HD>(v_tile, v_src ? v_src : p.v_pool, HD, TILE, valid, lane, 32);
+            if (k_src) {
+                load_tile_warp<HD, DKT, true>(k_tile, k_src, DKT, lane);
+                load_tile_warp<HD, DKT, true>(v_tile, v_src, DKT, lane);
+            } else {                                           // the page was given back: zeros
+                load_tile_warp<HD, DKT, false>(k_tile, p.k_pool, 0, lane);
+                load_tile_warp<HD, DKT, false>(v_tile, p.v_pool, 0, lane);
+            }
             cp_async_commit();
         }
     }
     chain_wait();
     chain_release();
     RowState<HD> st;
+    // rows 0..g-1 of the query tile are the g heads of this kv head; the rest are zero
+    load_tile<HD>(q_tile, p.qkv + (long long)q_begin * row_width + (long long)kvh * g * HD, HD, 16, g, tid, DW * 32);
+    if (holds_new) {
+        load_tile_warp<HD, DKT, false>(k_tile, k_src ? k_src : p.k_pool, valid, lane);
+        load_tile_warp<HD, DKT, false>(v_tile, v_src ? v_src : p.v_pool, valid, lane);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();                                           // the query tile is every warp's
     if (warp_active) {
-        // rows 0..g-1 of the query tile are the g heads of this kv head; the rest are zero
-        load_tile<HD>(q_tile, p.qkv + (long long)q_begin * row_width + (long long)kvh * g * HD, HD, 16, g, lane, 32);
-        if (holds_new) {
-            load_tile<HD>(k_tile, k_src ? k_src : p.k_pool, HD, TILE, valid, lane, 32);
-            load_tile<HD>(v_tile, v_src ? v_src : p.v_pool, HD, TILE, valid, lane, 32);
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
-        __syncwarp();
         uint32_t q[HD / 16][4];
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
@@ -369,7 +411,14 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
         }
         const int posv[2] = {pos, pos};
         const int lov[2] = {first_key, first_key};
-        attend_tile<HD, true>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
+        const bool masked = holds_new || key0 < first_key;     // else every key of the tile is visible
+        if (g <= 8) {
+            if (masked) attend_tile<HD, true, DKT, true, true>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
+            else attend_tile<HD, false, DKT, true, true>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
+        } else {
+            if (masked) attend_tile<HD, true, DKT, true, false>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
+            else attend_tile<HD, false, DKT, true, false>(st, q, k_tile, v_tile, key0, posv, lov, p.scale_log2, lane);
+        }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
@@ -377,36 +426,40 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
         }
     }
     __syncthreads();                                           // tiles are done with: reuse the memory for the merge
-    float* merge_o = reinterpret_cast<float*>(smem_raw);       // [warps][16 rows][HD]
-    float* merge_ml = merge_o + DW * 16 * HD;                   // [warps][16 rows][2]
+    // Only the g real rows are merged.  A row of the merge buffer is HD + 8 floats long, so that the
+    // 8-byte stores of a warp (rows lane / 4, dims 2 * (lane % 4) + 8 n) fall into different banks.
+    constexpr int RS = HD + 8;
+    float* merge_o = reinterpret_cast<float*>(smem_raw);       // [warps][16 rows][RS]
+    float* merge_ml = merge_o + DW * 16 * RS;                   // [warps][16 rows][2]
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int row = (lane >> 2) + r * 8;
-        float* o = merge_o + ((warp * 16 + row) * HD) + ((lane & 3) << 1);
+        if (row >= g) continue;
+        float* o = merge_o + ((warp * 16 + row) * RS) + ((lane & 3) << 1);
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) {
-            o[n * 8] = st.o[n][2 * r];
-            o[n * 8 + 1] = st.o[n][2 * r + 1];
-        }
-        if ((lane & 3) == 0) {
-            merge_ml[(warp * 16 + row) * 2] = st.m[r];
-            merge_ml[(warp * 16 + row) * 2 + 1] = st.l[r];
-        }
+        for (int n = 0; n < HD / 8; ++n) *reinterpret_cast<float2*>(o + n * 8) = make_float2(st.o[n][2 * r], st.o[n][2 * r + 1]);
+        if ((lane & 3) == 0) *reinterpret_cast<float2*>(merge_ml + (warp * 16 + row) * 2) = make_float2(st.m[r], st.l[r]);
     }
     __syncthreads();
-    // rows 0..g-1: merge the four warps in order, one thread per (row, dim)
+    // rows 0..g-1: merge the warps in order, one thread per (row, dim)
     for (int i = tid; i < g * HD; i += DW * 32) {
         const int row = i / HD, d = i % HD;
+        float2 ml[DW];
+        float ov[DW];
+#pragma unroll
+        for (int w = 0; w < DW; ++w) {
+            ml[w] = *reinterpret_cast<const float2*>(merge_ml + (w * 16 + row) * 2);
+            ov[w] = merge_o[(w * 16 + row) * RS + d];
+        }
         float m = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < DW; ++w) m = fmaxf(m, merge_ml[(w * 16 + row) * 2]);
+        for (int w = 0; w < DW; ++w) m = fmaxf(m, ml[w].x);
         float l = 0.f, o = 0.f;
 #pragma unroll
         for (int w = 0; w < DW; ++w) {
-            const float mw = merge_ml[(w * 16 + row) * 2];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - m);
-            l += merge_ml[(w * 16 + row) * 2 + 1] * f;
-            o += merge_o[(w * 16 + row) * HD + d] * f;
+            const float f = ml[w].x == -INFINITY ? 0.f : fast_exp2(ml[w].x - m);
+            l += ml[w].y * f;
+            o += ov[w] * f;
         }
         part_o[(long long)row * p.max_splits * HD + d] = o;
         if (d == 0) {
@@ -458,7 +511,7 @@ __global__ void decode_combine_kernel(AttnParams p) {
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
             if (ml[j].x == -INFINITY) continue;           // an empty split (its partial output was never written)
-            const float f = exp2f(ml[j].x - m);
+            const float f = fast_exp2(ml[j].x - m);
             l += ml[j].y * f;
             o += ov[j] * f;
         }
@@ -477,8 +530,8 @@ int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, c
         TS_LAUNCH_CHECK("prefill_attention");
     }
     if (min_q_len <= 1) {
-        const size_t tiles = (size_t)DW * (16 + 2 * TILE) * HD * sizeof(__nv_bfloat16);
-        const size_t merge = (size_t)(DW * 16 * HD + DW * 16 * 2) * sizeof(float);
+        const size_t tiles = (size_t)(16 + DW * 2 * DKT) * HD * sizeof(__nv_bfloat16);
+        const size_t merge = (size_t)(DW * 16 * (HD + 8) + DW * 16 * 2) * sizeof(float);
         const size_t smem = tiles > merge ? tiles : merge;
         auto kernel = decode_attention_kernel<HD>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
