@@ -154,6 +154,40 @@ def test_rope_store(ops, dtype, nh, nkv, hd, rot, page):
     assert torch.isnan(kp[:, 0].float()).all(), "the other cache entry of the group was touched"
 
 
+@pytest.mark.parametrize("nh, nkv, hd, page, hidden", [(4, 2, 16, 4, 64), (6, 2, 32, 32, 96), (5, 1, 48, 64, 160),
+                                                       (32, 8, 64, 16, 256), (8, 2, 128, 256, 512)])
+@pytest.mark.parametrize("q_lens, ctx_lens", [([1, 1, 1], [3, 70, 600]), ([3, 1, 5], [3, 66, 513]),
+                                              ([1] * 17, list(range(5, 22))), ([20, 12], [20, 300])])
+def test_projection_with_rotation_and_cache_write_in_its_epilogue(ops, nh, nkv, hd, page, hidden, q_lens, ctx_lens):
+    """The fused kernel for steps of a few tokens leaves exactly what the product and the rotary + store kernels leave."""
+    ctx = make_ctx(q_lens, ctx_lens)
+    pages_of = [-(-c // page) for c in ctx_lens]
+    order = torch.randperm(sum(pages_of) + 3, generator=torch.Generator().manual_seed(3)).tolist()
+    tables, used = [], 0
+    for n in pages_of:
+        tables.append(order[used:used + n])
+        used += n
+    T = ctx.num_tokens
+    x = rand((T, hidden), torch.bfloat16, 21).to(DEV)
+    w = rand(((nh + 2 * nkv) * hd, hidden), torch.bfloat16, 22, 0.1).to(DEV)
+    angles = torch.rand((max(ctx_lens) + 8, hd // 2), generator=torch.Generator().manual_seed(9)) * 6.0
+    table = torch.cat((angles.cos(), angles.sin()), dim=-1).float().to(DEV)
+    for use_table in (table, None):
+        apart = make_binding(len(order), 2, nkv, page, hd, torch.bfloat16, tables, entry=1)
+        fused = make_binding(len(order), 2, nkv, page, hd, torch.bfloat16, tables, entry=1)
+        want = ops.linear(x, w)
+        ops.rope_store(want, ctx, apart, use_table, nh, nkv, hd)
+        got = ops.linear_rope_store(x, w, ctx, fused, use_table, nh, nkv, hd)
+        assert got is not None, "the fused kernel takes up to 32 tokens of any head size in steps of 16"
+        assert torch.equal(got[:, : nh * hd], want[:, : nh * hd])
+        for a, b in ((apart.k_pool, fused.k_pool), (apart.v_pool, fused.v_pool)):
+            assert torch.equal(torch.isnan(a.float()), torch.isnan(b.float())), "other slots were written"
+            assert torch.equal(torch.nan_to_num(a.float()), torch.nan_to_num(b.float()))
+    # more tokens than the decode product takes: the caller falls back to the two kernels
+    many = rand((ops.skinny_max_rows + 1, hidden), torch.bfloat16, 23).to(DEV)
+    assert ops.linear_rope_store(many, w, ctx, fused, table, nh, nkv, hd) is None
+
+
 def plain_paged_attention(q, keys, values, ctx_lens, q_lens, scale, window):
     """q [T, nh, hd] float64; keys/values per sequence [ctx, nkv, hd]: whole-sequence attention, last q_len rows kept."""
     outs = []

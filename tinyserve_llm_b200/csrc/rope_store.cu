@@ -44,8 +44,8 @@ __global__ void rope_store_kernel(T* qkv, const int* __restrict__ positions, con
             float y1 = x1, y2 = x2;
             if (cs) {
                 const float c = cs[i], s = cs[half + i];
-                y1 = x1 * c - x2 * s;
-                y2 = x2 * c + x1 * s;
+                y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));       // every product rounded, as the reference does
+                y2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
             }
             const T o1 = from_float<T>(y1), o2 = from_float<T>(y2);
             if (!is_k) { h[i] = o1; h[i + half] = o2; }
@@ -131,8 +131,8 @@ __global__ void rope_store_vec_kernel(T* qkv, const int* __restrict__ positions,
                 const float x1 = to_float<T>(ae[e]), x2 = to_float<T>(be[e]);
                 float y1 = x1, y2 = x2;
                 if (cs) {
-                    y1 = x1 * c[e] - x2 * sn[e];
-                    y2 = x2 * c[e] + x1 * sn[e];
+                    y1 = __fsub_rn(__fmul_rn(x1, c[e]), __fmul_rn(x2, sn[e]));     // every product rounded, as the reference does
+                    y2 = __fadd_rn(__fmul_rn(x2, c[e]), __fmul_rn(x1, sn[e]));
                 }
                 oae[e] = from_float<T>(y1);
                 obe[e] = from_float<T>(y2);

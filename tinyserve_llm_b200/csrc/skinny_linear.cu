@@ -9,13 +9,31 @@
 // Epilogues: plain store, or SwiGLU: the CTA's 16 rows are 8 gate rows and the 8 up rows that belong
 // to them, and it stores round(silu(gate)) * up (model/llama.py:80-83 of the reference).
 //
+// A third epilogue serves the q/k/v projection of decode steps: the CTA's 16 rows are 8 features of one
+// head and their rotation partners half a head further on; it rotates q and k by the token's angles
+// (model/llama.py:20-49 of the reference: rotate-half, float32), writes q to the output and k and v
+// straight into the token's slot of the paged cache, which saves the separate rotary + store kernel.
+//
 // The split of K depends on N and K only, never on the number of rows of x, so a row's result does
 // not depend on what else is in the batch.
 #include "common.cuh"
 
 namespace {
 
-enum { EPI_STORE = 0, EPI_SWIGLU = 1 };
+enum { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ROPE = 2 };
+
+// What the rotary + store epilogue needs.  Index data is written by the host before the step.
+struct RopeArgs {
+    const int* positions;        // [M]
+    const int* seq_of_token;     // [M]; -1: a padding row (nothing is stored to the cache)
+    const float* table;          // [positions][hd]: cos of the hd/2 angles, then sin; null: no rotation
+    const int* block_table;      // [requests][table_width]
+    int table_width;
+    __nv_bfloat16* k_pool;
+    __nv_bfloat16* v_pool;
+    KVGeometry geo;
+    int nh, nkv, hd, write_kv;
+};
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -43,9 +61,11 @@ __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float
 template <int MT, int WARPS, int EPI, typename OUT, int UNROLL, int MINB>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x, OUT* __restrict__ y,
-                     int M, int N, int K, long long ldx, long long ldy, int inter) {
-    constexpr int ROWS = 16;                          // output rows of a CTA (8 pairs with the SwiGLU epilogue)
+                     int M, int N, int K, long long ldx, long long ldy, int inter, RopeArgs rope) {
+    constexpr int ROWS = 16;                          // output rows of a CTA (8 pairs with the SwiGLU and rotary epilogues)
     __shared__ float partial[WARPS][MT][32][4];
+    __shared__ float rope_cs[EPI == EPI_ROPE ? MT * 8 : 1][16];        // per token: 8 cos, 8 sin of this CTA's features
+    __shared__ long long rope_slot[EPI == EPI_ROPE ? MT * 8 : 1];      // per token: offset of its slot in the pools, -1: none
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, c = lane & 3;
     // the rows of W this thread streams (fragment rows r and r + 8)
@@ -56,6 +76,11 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
         rows_valid = min(8, inter - base);
         row_lo = base + min(r, rows_valid - 1);
         row_hi = (long long)inter + base + min(r, rows_valid - 1);
+    } else if (EPI == EPI_ROPE) {
+        const int blocks_per_head = rope.hd / 16;
+        rows_valid = 8;
+        row_lo = (long long)(blockIdx.x / blocks_per_head) * rope.hd + (blockIdx.x % blocks_per_head) * 8 + r;
+        row_hi = row_lo + rope.hd / 2;
     } else {
         const int base = blockIdx.x * ROWS;
         rows_valid = min(ROWS, N - base);
@@ -89,6 +114,33 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
         const int kb = min(u * WARPS + warp, kblocks - 1);
         wl[u] = ld_stream(w_lo + kb * 32);
         wh[u] = ld_stream(w_hi + kb * 32);
+    }
+    if (EPI == EPI_ROPE) {
+        // the token's angles and its slot in the cache: index data, read while the first weights are on their way
+        const int blocks_per_head = rope.hd / 16, head = blockIdx.x / blocks_per_head;
+        const int j0 = (blockIdx.x % blocks_per_head) * 8, half = rope.hd / 2;
+        for (int i = threadIdx.x; i < MT * 8 * 16; i += WARPS * 32) {
+            const int token = i >> 4, e = i & 15;
+            float v = e < 8 ? 1.f : 0.f;
+            if (token < M && rope.table != nullptr && head < rope.nh + rope.nkv)
+                v = rope.table[(long long)rope.positions[token] * rope.hd + (e < 8 ? j0 + e : half + j0 + e - 8)];
+            rope_cs[token][e] = v;
+        }
+        for (int token = threadIdx.x; token < MT * 8; token += WARPS * 32) {
+            long long slot = -1;
+            if (token < M && rope.write_kv && head >= rope.nh) {
+                const int seq = rope.seq_of_token[token];
+                if (seq >= 0) {
+                    const int pos = rope.positions[token];
+                    const int page = rope.block_table[(long long)seq * rope.table_width + pos / rope.geo.page_tokens];
+                    const int kvh = (head - rope.nh) % rope.nkv;
+                    if (page >= 0 && page < rope.geo.num_pages)
+                        slot = (long long)page * rope.geo.page_stride + rope.geo.entry_offset +
+                               ((long long)kvh * rope.geo.page_tokens + pos % rope.geo.page_tokens) * rope.hd;
+                }
+            }
+            rope_slot[token] = slot;
+        }
     }
     chain_wait();
     chain_release();      // after the wait: letting later kernels in sooner (before it) slowed the step by a third
@@ -150,6 +202,37 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
                 store_out<OUT>(y + (long long)token * ldy + blockIdx.x * 8 + row, silu * u);
             }
         }
+    } else if (EPI == EPI_ROPE) {
+        const int blocks_per_head = rope.hd / 16, head = blockIdx.x / blocks_per_head;
+        const int j0 = (blockIdx.x % blocks_per_head) * 8, half = rope.hd / 2;
+        for (int i = threadIdx.x; i < MT * 32 * 2; i += WARPS * 32) {
+            const int t = i / 64, l = (i / 2) % 32, e = i % 2;
+            float lo = 0.f, hi = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                lo += partial[w][t][l][e];
+                hi += partial[w][t][l][e + 2];
+            }
+            const int row = l >> 2, token = t * 8 + ((l & 3) << 1) + e;
+            if (token >= M) continue;
+            // the projection is materialised in bfloat16 before the rotation, as in the reference
+            const float x1 = round_to<__nv_bfloat16>(lo), x2 = round_to<__nv_bfloat16>(hi);
+            const float cs = rope_cs[token][row], sn = rope_cs[token][8 + row];
+            const float y1 = __fsub_rn(__fmul_rn(x1, cs), __fmul_rn(x2, sn));      // cos 1, sin 0 where nothing rotates
+            const float y2 = __fadd_rn(__fmul_rn(x2, cs), __fmul_rn(x1, sn));
+            const int feature = head * rope.hd + j0 + row;
+            if (head < rope.nh) {
+                store_out<OUT>(y + (long long)token * ldy + feature, y1);
+                store_out<OUT>(y + (long long)token * ldy + feature + half, y2);
+            } else {
+                const long long slot = rope_slot[token];
+                if (slot >= 0) {
+                    __nv_bfloat16* pool = head < rope.nh + rope.nkv ? rope.k_pool : rope.v_pool;
+                    pool[slot + j0 + row] = __float2bfloat16_rn(y1);
+                    pool[slot + j0 + row + half] = __float2bfloat16_rn(y2);
+                }
+            }
+        }
     } else {
         constexpr int PER = 4;
         for (int i = threadIdx.x; i < MT * 32 * PER; i += WARPS * 32) {
@@ -165,21 +248,21 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
 
 template <int MT, int WARPS, int EPI, typename OUT, int UNROLL, int MINB>
 int launch(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
-           cudaStream_t stream) {
+           cudaStream_t stream, const RopeArgs& rope) {
     const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
     TS_CHAINED_CHECK("skinny_linear", launch_chained(skinny_linear_kernel<MT, WARPS, EPI, OUT, UNROLL, MINB>,
                                                      dim3(tiles), dim3(WARPS * 32), 0, stream, (const __nv_bfloat16*)W,
-                                                     (const __nv_bfloat16*)x, (OUT*)y, M, N, K, ldx, ldy, inter));
+                                                     (const __nv_bfloat16*)x, (OUT*)y, M, N, K, ldx, ldy, inter, rope));
     return 0;
 }
 
 template <int WARPS, int EPI, typename OUT, int UNROLL, int MINB>
 int dispatch_m(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
-               cudaStream_t stream) {
-    if (M <= 8) return launch<1, WARPS, EPI, OUT, UNROLL, MINB>(W, x, y, M, N, K, ldx, ldy, inter, stream);
-    if (M <= 16) return launch<2, WARPS, EPI, OUT, UNROLL, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+               cudaStream_t stream, const RopeArgs& rope) {
+    if (M <= 8) return launch<1, WARPS, EPI, OUT, UNROLL, MINB>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    if (M <= 16) return launch<2, WARPS, EPI, OUT, UNROLL, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
     // 32 rows of x with 16 warps: fewer loads in flight, to stay within the 128 registers a thread of 512 can have
-    return launch<4, WARPS, EPI, OUT, (WARPS > 8 ? 2 : UNROLL), 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    return launch<4, WARPS, EPI, OUT, (WARPS > 8 ? 2 : UNROLL), 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
 }
 
 int g_warps_override = 0;       // tuning aid: 4, 8 or 16 forces plain 16-row tiles with that many warps; 0: the rules below
@@ -193,16 +276,16 @@ int g_warps_override = 0;       // tuning aid: 4, 8 or 16 forces plain 16-row ti
 //   were no faster: the SMs that get two of them take as long as one 16-row tile.)
 template <int EPI, typename OUT>
 int dispatch_warps(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
     const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
     const int kblocks = K / 32;
-    if (g_warps_override == 4) return dispatch_m<4, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
-    if (g_warps_override == 8) return dispatch_m<8, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
-    if (g_warps_override == 16) return dispatch_m<16, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+    if (g_warps_override == 4) return dispatch_m<4, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    if (g_warps_override == 8) return dispatch_m<8, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    if (g_warps_override == 16) return dispatch_m<16, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
     if (tiles > 296 || kblocks < 32)
-        return dispatch_m<4, EPI, OUT, 2, 7>(W, x, y, M, N, K, ldx, ldy, inter, stream);
-    if (tiles > 148) return dispatch_m<8, EPI, OUT, 4, 2>(W, x, y, M, N, K, ldx, ldy, inter, stream);
-    return dispatch_m<16, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream);
+        return dispatch_m<4, EPI, OUT, 2, 7>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    if (tiles > 148) return dispatch_m<8, EPI, OUT, 4, 2>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    return dispatch_m<16, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
 }
 
 }  // namespace
@@ -231,4 +314,41 @@ TS_API int ts_skinny_linear(const void* W, const void* x, void* y, int M, int N,
     if (out_dtype == TS_BF16) return dispatch_warps<EPI_STORE, __nv_bfloat16>(W, x, y, M, N, K, ldx, ldy, 0, stream);
     if (out_dtype == TS_F32) return dispatch_warps<EPI_STORE, float>(W, x, y, M, N, K, ldx, ldy, 0, stream);
     return ts_fail("skinny_linear: unknown output dtype code %d", out_dtype);
+}
+
+// The q/k/v projection of a decode step with rotary embedding and the write into the paged cache in
+// its epilogue: qkv[M, (nh + 2 nkv) hd] receives the rotated q (its k and v columns are not written);
+// k (rotated) and v go to the slot of each token's position.  The rotary width must be the head
+// size, a multiple of 16.  Pools are bfloat16, laid out as KVGeometry says.
+TS_API int ts_skinny_qkv_rope_store(const void* W, const void* x, void* qkv, int M, int K, long long ldx,
+                                    const int* positions, const int* seq_of_token, const float* table, int table_rows,
+                                    int rot, const int* block_table, int table_width, void* k_pool, void* v_pool,
+                                    long long page_stride, long long entry_offset, int page_tokens, int num_pages,
+                                    int nh, int nkv, int hd, int write_kv, cudaStream_t stream) {
+    TS_REQUIRE(M >= 0 && K > 0 && nh > 0 && nkv > 0 && hd > 0, "skinny_qkv_rope_store: bad sizes");
+    TS_REQUIRE(M <= ts_skinny_linear_max_rows(), "skinny_qkv_rope_store: %d rows of x; the kernel takes up to %d", M,
+               ts_skinny_linear_max_rows());
+    TS_REQUIRE(K % 32 == 0, "skinny_qkv_rope_store: K=%d is not a multiple of 32", K);
+    TS_REQUIRE(hd % 16 == 0, "skinny_qkv_rope_store: head size %d is not a multiple of 16", hd);
+    TS_REQUIRE(table == nullptr || rot == hd, "skinny_qkv_rope_store: rotary width %d must equal the head size %d", rot, hd);
+    TS_REQUIRE(table == nullptr || table_rows > 0, "skinny_qkv_rope_store: empty rotary table");
+    TS_REQUIRE(ldx % 8 == 0 && ((uintptr_t)W % 16 == 0) && ((uintptr_t)x % 16 == 0),
+               "skinny_qkv_rope_store: operands must be 16-byte aligned");
+    TS_REQUIRE(page_tokens > 0 && num_pages > 0 && table_width > 0, "skinny_qkv_rope_store: bad cache geometry");
+    if (M == 0) return 0;
+    RopeArgs rope;
+    rope.positions = positions;
+    rope.seq_of_token = seq_of_token;
+    rope.table = table;
+    rope.block_table = block_table;
+    rope.table_width = table_width;
+    rope.k_pool = (__nv_bfloat16*)k_pool;
+    rope.v_pool = (__nv_bfloat16*)v_pool;
+    rope.geo = KVGeometry{page_stride, entry_offset, page_tokens, num_pages};
+    rope.nh = nh;
+    rope.nkv = nkv;
+    rope.hd = hd;
+    rope.write_kv = write_kv;
+    const int N = (nh + 2 * nkv) * hd;
+    return dispatch_warps<EPI_ROPE, __nv_bfloat16>(W, x, qkv, M, N, K, ldx, N, 0, stream, rope);
 }

@@ -137,6 +137,34 @@ class Ops:
                    c_int(binding.page_tokens), c_int(binding.num_pages), c_int(qkv.shape[0]), c_int(nh), c_int(nkv),
                    c_int(hd), c_int(1 if binding.writes else 0), c_int(_DTYPE_CODE[qkv.dtype]), _stream())
 
+    def linear_rope_store(self, x: torch.Tensor, weight: torch.Tensor, ctx, binding, table: torch.Tensor | None,
+                          nh: int, nkv: int, hd: int) -> torch.Tensor | None:
+        """
+        The q/k/v projection of a step of a few tokens with the rotation and the cache write in its
+        epilogue: returns qkv [T, (nh + 2 nkv) * hd] whose q columns are rotated (k and v are in
+        the cache only), or None where the fused kernel does not take the case (then: `linear`,
+        `rope_store`).  Takes bfloat16, as many tokens as the decode product does, a rotary width equal to the head size.
+        """
+        if (not self._skinny(x, weight) or hd % 16 or binding.k_pool.dtype != torch.bfloat16
+                or binding.block_table is None or (table is not None and table.shape[1] != hd)):
+            return None
+        self._check(x, "x", torch.bfloat16, 2)
+        self._check(weight, "weight", torch.bfloat16, 2)
+        if tuple(weight.shape) != ((nh + 2 * nkv) * hd, x.shape[1]):
+            raise KernelError(f"linear_rope_store: weight is {tuple(weight.shape)}, expected {((nh + 2 * nkv) * hd, x.shape[1])}")
+        rows = 0
+        if table is not None:
+            self._check(table, "rotary table", torch.float32, 2)
+            rows = table.shape[0]
+        qkv = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
+        self._call("ts_skinny_qkv_rope_store", _ptr(weight), _ptr(x), _ptr(qkv), c_int(x.shape[0]), c_int(x.shape[1]),
+                   c_longlong(x.stride(0)), _ptr(ctx.positions), _ptr(ctx.seq_of_token), _ptr(table), c_int(rows),
+                   c_int(hd), _ptr(binding.block_table), c_int(binding.table_width), _ptr(binding.k_pool),
+                   _ptr(binding.v_pool), c_longlong(binding.page_stride), c_longlong(binding.entry_offset),
+                   c_int(binding.page_tokens), c_int(binding.num_pages), c_int(nh), c_int(nkv), c_int(hd),
+                   c_int(1 if binding.writes else 0), _stream())
+        return qkv
+
     def paged_attention(self, qkv: torch.Tensor, ctx, binding, nh: int, nkv: int, hd: int, scale: float,
                         window: int, generic: bool = False) -> torch.Tensor:
         """

@@ -48,15 +48,18 @@ class PagedAttention(Mixer):
 
     def forward(self, x: torch.Tensor, ctx, binding) -> torch.Tensor:
         spec, ops = self.spec, self.rt.ops
-        qkv = self.qkv(x)                                       # [T, (nh + 2 nkv) * hd]
-        table = None
-        if self.position is not None:
-            table = self.position.table
-            if table is None:                                   # a position part that edits q and k itself
+        table = self.position.table if self.position is not None else None
+        qkv = None
+        if self.position is None or table is not None:          # a few tokens: projection, rotation and cache write in one kernel
+            qkv = ops.linear_rope_store(x, self.qkv.weight, ctx, binding, table, spec.num_heads, spec.num_kv_heads,
+                                        spec.head_dim)
+        if qkv is None:
+            qkv = self.qkv(x)                                   # [T, (nh + 2 nkv) * hd]
+            if self.position is not None and table is None:     # a position part that edits q and k itself
                 nq = spec.num_heads * spec.head_dim
                 nk = spec.num_kv_heads * spec.head_dim
                 self.position.apply(qkv[:, :nq], qkv[:, nq:nq + nk], ctx)
-        ops.rope_store(qkv, ctx, binding, table, spec.num_heads, spec.num_kv_heads, spec.head_dim)
+            ops.rope_store(qkv, ctx, binding, table, spec.num_heads, spec.num_kv_heads, spec.head_dim)
         o = ops.paged_attention(qkv, ctx, binding, spec.num_heads, spec.num_kv_heads, spec.head_dim,
                                 spec.scale, spec.window)         # [T, nh * hd]
         return self.out(o)
