@@ -162,13 +162,16 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
 
-    const int seq = blockIdx.z, head = blockIdx.y;
+    // blockIdx.x (which varies fastest in the order CTAs are handed out) is the head, blockIdx.y counts the
+    // request's tiles from its last: the tile with the most keys of every head starts first, and
+    // the short ones fill the SMs as the long ones finish.
+    const int seq = blockIdx.z, head = blockIdx.x;
     chain_wait();                                    // q, k and v of the step come from kernels ahead on the stream
     chain_release();
     const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
     if (q_len <= 1) return;                          // decode rows go to the split-key kernels
     const int tiles = (q_len + QROWS - 1) / QROWS;
-    const int tile_index = tiles - 1 - (int)blockIdx.x;          // long tiles first
+    const int tile_index = tiles - 1 - (int)blockIdx.y;
     if (tile_index < 0) return;
     const int ctx = p.ctx_lens[seq];
     const int row0 = tile_index * QROWS;
@@ -408,7 +411,8 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
                                         int nh, int nkv, int hd, float scale, int* error, cudaStream_t stream) {
     TS_REQUIRE(ts_attention_tcgen05_supported(hd, page_tokens, nh, nkv, 0), "attention_tcgen05: sizes not taken (head_dim %d, page %d)", hd, page_tokens);
     TS_REQUIRE(error != nullptr, "attention_tcgen05: an error word is needed");
-    TS_REQUIRE(num_seqs <= 65535 && nh <= 65535, "attention_tcgen05: more than 65535 requests or heads in a step");
+    TS_REQUIRE(num_seqs <= 65535 && (max_q_len + QROWS - 1) / QROWS <= 65535,
+               "attention_tcgen05: more than 65535 requests, or tiles of a request, in a step");
     TS_REQUIRE(((uintptr_t)qkv % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0),
                "attention_tcgen05: operands must be 16-byte aligned");
     if (num_seqs == 0 || max_q_len <= 1) return 0;
@@ -436,7 +440,7 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
     const size_t smem = (size_t)Q_BYTES + 2 * STAGE_BYTES + 1024;
     auto kernel = prefill_attention_tcgen05_kernel;
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    dim3 grid((max_q_len + QROWS - 1) / QROWS, nh, num_seqs);
+    dim3 grid(nh, (max_q_len + QROWS - 1) / QROWS, num_seqs);
     TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(192), smem, stream, map_q, map_k, map_v, p));
     return 0;
 }
