@@ -307,7 +307,7 @@ def run_ours(args) -> dict:
             "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "vocab_size": cfg["vocab_size"], "global_batch": BATCH, "seq_len": CONTEXT,
             "points_context_len": point_context, "prefill_tokens": PREFILL_TOKENS, "page_tokens": PAGE,
-            "parallelism": "single GPU", "cuda_graphs": bool(graph), "l2": "inputs larger than L2 (weights 2.5 GB per step)",
+            "parallelism": "single GPU", "cuda_graphs": bool(graph), "l2": f"inputs larger than L2 (weights {weight_bytes(cfg, layers) / 1e9:.1f} GB per step)",
             "peaks": peak_kind,
         },
         "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
