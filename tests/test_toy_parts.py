@@ -3,6 +3,8 @@ Generality of the parts: a toy mixer with fixed-size per-request state of its ow
 registered, built into a model beside attention layers and stepped through the engine (portions,
 decoding, several requests, a fork) without any change to the framework's files.  The run list of
 that model also names a block twice and lets one execution read the cache another one wrote.
+Further down: layers with a window in a layer group of their own, and two more toy parts, a
+feed-forward with routing and a position encoding that edits q and k itself.
 """
 
 from dataclasses import dataclass, field
@@ -253,4 +255,168 @@ def test_window_layers_have_pages_of_their_own_and_give_them_back(dtype, hd, pag
     assert manager.counters.window_releases == passed
     assert manager.available_pages()[1] > manager.available_pages()[0]
     manager.release("w")
+    assert manager.stats().pages_in_use == 0
+
+
+def test_toy_routed_feed_forward_and_toy_position_encoding_are_registered_built_and_stepped():
+    """
+    Two more toy parts, defined here and nowhere in the framework: a feed-forward that routes each
+    token to two of three experts (router logits and softmax in float32), and a position encoding
+    that rotates adjacent pairs of dims and so edits q and k itself instead of handing the kernels a
+    table.  A model with one layer of each beside a stock layer is stepped in portions and token by
+    token, two requests side by side, and equals a float64 calculation of the same formulas.
+    """
+    import plain_llama as plain
+    from tinyserve_llm_b200.config.spec import (AttentionSpec, BlockSpec, GatedMLPSpec, ModelSpec, PartSpec,
+                                                RMSNormSpec, RotarySpec, RunEntry)
+    from tinyserve_llm_b200.engine.loading import build_cache
+    from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
+    from tinyserve_llm_b200.ops import get_ops
+    from tinyserve_llm_b200.parts.base import FeedForward, PositionEncoding, Runtime, TensorDecl, register_part
+    from tinyserve_llm_b200.parts.model import DecoderModel, declared_tensors
+    from tinyserve_llm_b200.weights import random_tensors
+
+    hidden, heads, kv, hd, inter, vocab, experts, base = 64, 4, 2, 16, 48, 89, 3, 500.0
+
+    @dataclass(frozen=True)
+    class RoutedSpec(PartSpec):
+        kind: str = field(init=False, default="toy_routed")
+        hidden_size: int = 0
+        intermediate_size: int = 0
+        num_experts: int = 0
+        top_k: int = 1
+
+    @register_part("feed_forward", "toy_routed")
+    class RoutedFeedForward(FeedForward):
+        @classmethod
+        def declare(cls, spec):
+            out = {"router.weight": TensorDecl((spec.num_experts, spec.hidden_size))}
+            for e in range(spec.num_experts):
+                out[f"experts.{e}.up.weight"] = TensorDecl((spec.intermediate_size, spec.hidden_size))
+                out[f"experts.{e}.down.weight"] = TensorDecl((spec.hidden_size, spec.intermediate_size))
+            return out
+
+        def __init__(self, spec, tensors, rt):
+            super().__init__(spec, tensors, rt)
+            self.router = tensors["router.weight"].to(rt.device, torch.float32)
+            self.up = [tensors[f"experts.{e}.up.weight"].to(rt.device, rt.dtype) for e in range(spec.num_experts)]
+            self.down = [tensors[f"experts.{e}.down.weight"].to(rt.device, rt.dtype) for e in range(spec.num_experts)]
+
+        def forward(self, x, ctx):
+            probs = torch.softmax(x.float() @ self.router.T, dim=-1)
+            top, chosen = probs.topk(self.spec.top_k, dim=-1)
+            top = top / top.sum(-1, keepdim=True)
+            out = torch.zeros_like(x, dtype=torch.float32)
+            for e in range(self.spec.num_experts):
+                weight = (top * (chosen == e)).sum(-1, keepdim=True)          # 0 for tokens not routed to e
+                out += weight * (torch.relu(x @ self.up[e].T) @ self.down[e].T).float()
+            return out.to(x.dtype)
+
+    @dataclass(frozen=True)
+    class PairRotarySpec(PartSpec):
+        kind: str = field(init=False, default="toy_pair_rotary")
+        head_dim: int = 0
+        base: float = 10000.0
+
+    @register_part("position", "toy_pair_rotary")
+    class PairRotary(PositionEncoding):
+        """Rotates dims (2i, 2i+1) of every head by position * base^(-2i / head_dim); no table for the kernels."""
+
+        def apply(self, q, k, ctx):
+            hd_ = self.spec.head_dim
+            inv = self.spec.base ** (-torch.arange(0, hd_, 2, device=q.device, dtype=torch.float32) / hd_)
+            ang = ctx.positions.float()[:, None] * inv[None, :]
+            cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+            for t in (q, k):
+                v = t.view(t.shape[0], -1, hd_ // 2, 2).float()
+                a, b = v[..., 0].clone(), v[..., 1].clone()
+                v2 = torch.stack((a * cos - b * sin, b * cos + a * sin), dim=-1)
+                t.copy_(v2.view(t.shape[0], -1).to(t.dtype))
+
+    rotary = RotarySpec(head_dim=hd, theta=1000.0, max_positions=256)
+    attn = AttentionSpec(hidden_size=hidden, num_heads=heads, num_kv_heads=kv, head_dim=hd, scale=hd ** -0.5, position=rotary)
+    attn_pairs = AttentionSpec(hidden_size=hidden, num_heads=heads, num_kv_heads=kv, head_dim=hd, scale=hd ** -0.5,
+                               position=PairRotarySpec(head_dim=hd, base=base))
+    mlp, norm = GatedMLPSpec(hidden_size=hidden, intermediate_size=inter), RMSNormSpec(size=hidden, eps=1e-5)
+    routed = RoutedSpec(hidden_size=hidden, intermediate_size=inter, num_experts=experts, top_k=2)
+    blocks = (BlockSpec("pre_norm", attn_pairs, routed, norm, norm, prefix="layers.0.", feed_forward_prefix="moe."),
+              BlockSpec("pre_norm", attn, mlp, norm, norm, prefix="layers.1."))
+    spec = ModelSpec("ToyRouted", vocab, hidden, blocks, (RunEntry(0, 0), RunEntry(1, 1)), norm, "embed.weight",
+                     "final_norm.", None, 256, -1)
+    declared = declared_tensors(spec)
+    assert "layers.0.moe.router.weight" in declared and "layers.0.moe.experts.2.down.weight" in declared
+    tensors = dict(random_tensors(declared, 11, std=0.1, unit_std=0.2))
+    device = torch.device("cuda", torch.cuda.current_device())
+    model = DecoderModel(spec, {k: v.to(device) for k, v in tensors.items()},
+                         Runtime(dtype=torch.float32, device=device, ops=get_ops()))
+    assert not model.graph_safe
+    layout, manager, storage = build_cache(model, 16, 16)
+    runner = StepRunner(model, manager, storage)
+
+    def plain_logits(ids):
+        w = {k: v.double() for k, v in tensors.items()}
+        T, positions = len(ids), torch.arange(len(ids))
+        x, residual = w["embed.weight"][torch.tensor(ids)], None
+        # layer 0: pair rotary + routed feed-forward
+        lw = {k[len("layers.0."):]: v for k, v in w.items() if k.startswith("layers.0.")}
+        n, residual = plain.rms_norm(x, lw["input_layernorm.weight"], 1e-5, "float32"), x
+        inv = base ** (-torch.arange(0, hd, 2, dtype=torch.float64) / hd)
+        ang = positions.double()[:, None] * inv[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+
+        def rotate(t):
+            v = t.view(T, -1, hd // 2, 2)
+            return torch.stack((v[..., 0] * cos - v[..., 1] * sin, v[..., 1] * cos + v[..., 0] * sin), dim=-1).view(T, -1, hd)
+
+        q = rotate(plain.linear(n, lw["self_attn.q_proj.weight"], "float32"))
+        k = rotate(plain.linear(n, lw["self_attn.k_proj.weight"], "float32"))
+        v = plain.linear(n, lw["self_attn.v_proj.weight"], "float32").view(T, kv, hd)
+        o = plain.causal_attention(q, k, v, hd ** -0.5, "float32", 0).reshape(T, heads * hd)
+        a = plain.linear(o, lw["self_attn.o_proj.weight"], "float32")
+        n, residual = plain.add_rms_norm(a, residual, lw["post_attention_layernorm.weight"], 1e-5, "float32")
+        probs = torch.softmax(n @ lw["moe.router.weight"].T, dim=-1)
+        top, chosen = probs.topk(2, dim=-1)
+        top = top / top.sum(-1, keepdim=True)
+        x = torch.zeros_like(n)
+        for e in range(experts):
+            weight = (top * (chosen == e)).sum(-1, keepdim=True)
+            x += weight * (torch.relu(n @ lw[f"moe.experts.{e}.up.weight"].T) @ lw[f"moe.experts.{e}.down.weight"].T)
+        # layer 1: the stock parts
+        lw = {k[len("layers.1."):]: v for k, v in w.items() if k.startswith("layers.1.")}
+        cfg = {"num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd, "hidden_size": hidden,
+               "rope_theta": 1000.0, "max_position_embeddings": 256}
+        n, residual = plain.add_rms_norm(x, residual, lw["input_layernorm.weight"], 1e-5, "float32")
+        a, _ = plain.attention_block(cfg, lw, n, positions, "float32")
+        n, residual = plain.add_rms_norm(a, residual, lw["post_attention_layernorm.weight"], 1e-5, "float32")
+        x = plain.mlp_block(lw, n, "float32")
+        return plain.add_rms_norm(x, residual, w["final_norm.weight"], 1e-5, "float32")[0] @ w["embed.weight"].T
+
+    g = torch.Generator().manual_seed(2)
+    a = torch.randint(0, vocab, (45,), generator=g).tolist()
+    b = torch.randint(0, vocab, (30,), generator=g).tolist()
+
+    def feed(parts):
+        entries = []
+        for name, tokens in parts:
+            if name in manager.seqs:
+                manager.extend(name, tokens)
+            else:
+                assert manager.admit(name, tokens)
+            entries.append(StepEntry(name, tokens, list(range(len(tokens)))))
+        logits = runner.step(entries).cpu().double()
+        for e in entries:
+            manager.commit(e.seq_id, len(e.tokens))
+        return logits
+
+    got_a = [feed([("a", a[:17])])]
+    both = feed([("a", a[17:19]), ("b", b[:20])])                  # two tokens of a beside a portion of b
+    got_a.append(both[:2])
+    got_b = [both[2:]]
+    for i in range(10):                                            # token by token, side by side
+        both = feed([("b", b[20 + i:21 + i]), ("a", a[19 + i:20 + i])])
+        got_b.append(both[:1]), got_a.append(both[1:])
+    got_a.append(feed([("a", a[29:])]))
+    torch.testing.assert_close(torch.cat(got_a), plain_logits(a), atol=3e-5, rtol=1e-5)
+    torch.testing.assert_close(torch.cat(got_b), plain_logits(b), atol=3e-5, rtol=1e-5)
+    manager.release("a"), manager.release("b")
     assert manager.stats().pages_in_use == 0
