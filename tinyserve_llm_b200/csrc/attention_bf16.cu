@@ -224,6 +224,7 @@ struct AttnParams {
     int num_seqs, nh, nkv;
     float scale_log2;
     int window;
+    const int* prefill_seqs;   // requests that feed more than one token, for the prefill grid; null: every request
     // decode only
     float* partial_o;      // [seq][head][split][HD]
     float* partial_ml;     // [seq][head][split][2]
@@ -246,7 +247,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);             // [64][HD]
     __nv_bfloat16* kv_tiles = q_tile + TILE * HD;                                     // 2 stages x (K, V) x [64][HD]
-    const int seq = blockIdx.z, head = blockIdx.y;
+    const int seq = p.prefill_seqs ? p.prefill_seqs[blockIdx.z] : (int)blockIdx.z, head = blockIdx.y;
     const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
     if (q_len <= 1) return;                                                           // decode rows go to the other kernel
     const int tiles = (q_len + TILE - 1) / TILE;
@@ -520,12 +521,12 @@ __global__ void decode_combine_kernel(AttnParams p) {
 }
 
 template <int HD>
-int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, cudaStream_t stream) {
+int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, int num_prefill_seqs, cudaStream_t stream) {
     if (max_q_len > 1) {
         const size_t smem = (size_t)(TILE * HD + 4 * TILE * HD) * sizeof(__nv_bfloat16);
         auto kernel = prefill_attention_kernel<HD>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        dim3 grid((max_q_len + TILE - 1) / TILE, p.nh, p.num_seqs);
+        dim3 grid((max_q_len + TILE - 1) / TILE, p.nh, p.prefill_seqs ? num_prefill_seqs : p.num_seqs);
         kernel<<<grid, 128, smem, stream>>>(p);
         TS_LAUNCH_CHECK("prefill_attention");
     }
@@ -559,12 +560,15 @@ TS_API int ts_attention_bf16_supported(int hd, int page_tokens, int nh, int nkv)
 
 // max_q_len / min_q_len: longest and shortest number of tokens a request feeds in this step (which
 // kernels run); max_ctx_len: an upper bound of the requests' lengths (the decode grid and scratch).
+// prefill_seqs (optional, device): the requests that feed more than one token, so that the prefill
+// grid has no CTAs for the others (a CTA that only finds out it has nothing to do still holds its
+// shared memory while it does).
 TS_API int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_pool, const void* v_pool,
                                    long long page_stride, long long entry_offset, int page_tokens, int num_pages,
                                    const int* block_table, int table_width, const int* cu_q, const int* ctx_lens,
                                    int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv, int hd,
                                    float scale, int window, float* scratch, long long scratch_floats,
-                                   cudaStream_t stream) {
+                                   const int* prefill_seqs, int num_prefill_seqs, cudaStream_t stream) {
     TS_REQUIRE(ts_attention_bf16_supported(hd, page_tokens, nh, nkv),
                "paged_attention_bf16: head_dim %d / page %d / heads %d:%d is not taken by the tensor-core kernels", hd,
                page_tokens, nh, nkv);
@@ -587,6 +591,10 @@ TS_API int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_poo
     p.scale_log2 = scale * LOG2E;
     p.window = window;
     p.max_splits = (max_ctx_len + SPLIT - 1) / SPLIT;
+    p.prefill_seqs = prefill_seqs;
+    TS_REQUIRE(prefill_seqs == nullptr || (num_prefill_seqs >= 0 && num_prefill_seqs <= num_seqs),
+               "paged_attention_bf16: %d prefill requests of %d", num_prefill_seqs, num_seqs);
+    if (prefill_seqs != nullptr && num_prefill_seqs == 0) max_q_len = min_q_len < 1 ? min_q_len : 1;   // nothing for the prefill kernel
     p.partial_o = scratch;
     p.partial_ml = scratch ? scratch + (long long)num_seqs * nh * p.max_splits * hd : nullptr;
     if (min_q_len <= 1) {
@@ -595,6 +603,6 @@ TS_API int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_poo
         TS_REQUIRE((long long)table_width * page_tokens >= max_ctx_len,
                    "paged_attention_bf16: block tables of %d pages do not reach %d tokens", table_width, max_ctx_len);
     }
-    if (hd == 64) return launch<64>(p, max_q_len, min_q_len, max_ctx_len, stream);
-    return launch<128>(p, max_q_len, min_q_len, max_ctx_len, stream);
+    if (hd == 64) return launch<64>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
+    return launch<128>(p, max_q_len, min_q_len, max_ctx_len, num_prefill_seqs, stream);
 }

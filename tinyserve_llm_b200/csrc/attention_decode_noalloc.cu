@@ -17,7 +17,7 @@ extern "C" int ts_paged_attention_bf16(const void* qkv, void* out, const void* k
                                        const int* block_table, int table_width, const int* cu_q, const int* ctx_lens,
                                        int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv,
                                        int hd, float scale, int window, float* scratch, long long scratch_floats,
-                                       cudaStream_t stream);
+                                       const int* prefill_seqs, int num_prefill_seqs, cudaStream_t stream);
 
 namespace {
 
@@ -63,5 +63,5 @@ TS_API int ts_decode_attention_bf16_noalloc(const void* qkv, void* out, const vo
     if (scratch_on_current_device(&scratch) != 0) return 1;
     return ts_paged_attention_bf16(qkv, out, k_pool, v_pool, page_stride, entry_offset, page_tokens, num_pages,
                                    block_table, table_width, cu_q, ctx_lens, num_seqs, /*max_q_len=*/1, /*min_q_len=*/1,
-                                   max_ctx_len, nh, nkv, hd, scale, window, scratch, TS_NOALLOC_SCRATCH_FLOATS, stream);
+                                   max_ctx_len, nh, nkv, hd, scale, window, scratch, TS_NOALLOC_SCRATCH_FLOATS, nullptr, 0, stream);
 }

@@ -146,6 +146,7 @@ struct FlashParams {
     int table_width;
     const int* cu_q;
     const int* ctx_lens;
+    const int* prefill_seqs;          // requests that feed more than one token; null: every request has CTAs
     int nh, nkv;
     int page_tokens, num_pages;
     int entries, entry;               // cache entries of the layer group; this layer's index among them
@@ -165,7 +166,7 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
     // blockIdx.x (which varies fastest in the order CTAs are handed out) is the head, blockIdx.y counts the
     // request's tiles from its last: the tile with the most keys of every head starts first, and
     // the short ones fill the SMs as the long ones finish.
-    const int seq = blockIdx.z, head = blockIdx.x;
+    const int seq = p.prefill_seqs ? p.prefill_seqs[blockIdx.z] : (int)blockIdx.z, head = blockIdx.x;
     chain_wait();                                    // q, k and v of the step come from kernels ahead on the stream
     chain_release();
     const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
@@ -404,11 +405,13 @@ TS_API int ts_attention_tcgen05_supported(int hd, int page_tokens, int nh, int n
 }
 
 // Prompt portions (requests that feed more than one token) of a step; requests that feed one token
-// are left to the decode kernels.  The pools are [pages][entries][kv heads][page_tokens][64].
+// are left to the decode kernels.  prefill_seqs (optional, device) lists the former, so that the grid
+// has no CTAs for the latter.  The pools are [pages][entries][kv heads][page_tokens][64].
 TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* k_pool, const void* v_pool, int num_pages,
                                         int entries, int entry, int page_tokens, const int* block_table, int table_width,
                                         const int* cu_q, const int* ctx_lens, int num_seqs, int num_tokens, int max_q_len,
-                                        int nh, int nkv, int hd, float scale, int* error, cudaStream_t stream) {
+                                        int nh, int nkv, int hd, float scale, const int* prefill_seqs, int num_prefill_seqs,
+                                        int* error, cudaStream_t stream) {
     TS_REQUIRE(ts_attention_tcgen05_supported(hd, page_tokens, nh, nkv, 0), "attention_tcgen05: sizes not taken (head_dim %d, page %d)", hd, page_tokens);
     TS_REQUIRE(error != nullptr, "attention_tcgen05: an error word is needed");
     TS_REQUIRE(num_seqs <= 65535 && (max_q_len + QROWS - 1) / QROWS <= 65535,
@@ -416,6 +419,9 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
     TS_REQUIRE(((uintptr_t)qkv % 16 == 0) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0),
                "attention_tcgen05: operands must be 16-byte aligned");
     if (num_seqs == 0 || max_q_len <= 1) return 0;
+    TS_REQUIRE(prefill_seqs == nullptr || (num_prefill_seqs >= 0 && num_prefill_seqs <= num_seqs),
+               "attention_tcgen05: %d prefill requests of %d", num_prefill_seqs, num_seqs);
+    if (prefill_seqs != nullptr && num_prefill_seqs == 0) return 0;
     const long long pool_rows = (long long)num_pages * entries * nkv * page_tokens;
     TS_REQUIRE(pool_rows < 0x7fffffffll, "attention_tcgen05: the pool has too many rows for 32-bit TMA coordinates");
     const long long row_width = (long long)(nh + 2 * nkv) * hd;
@@ -429,6 +435,7 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
     p.table_width = table_width;
     p.cu_q = cu_q;
     p.ctx_lens = ctx_lens;
+    p.prefill_seqs = prefill_seqs;
     p.nh = nh;
     p.nkv = nkv;
     p.page_tokens = page_tokens;
@@ -440,7 +447,7 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
     const size_t smem = (size_t)Q_BYTES + 2 * STAGE_BYTES + 1024;
     auto kernel = prefill_attention_tcgen05_kernel;
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    dim3 grid(nh, (max_q_len + QROWS - 1) / QROWS, num_seqs);
+    dim3 grid(nh, (max_q_len + QROWS - 1) / QROWS, prefill_seqs ? num_prefill_seqs : num_seqs);
     TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(192), smem, stream, map_q, map_k, map_v, p));
     return 0;
 }

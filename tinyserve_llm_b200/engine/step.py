@@ -61,6 +61,7 @@ class StepContext:
         self.ctx_lens: torch.Tensor = None        # int32 [S]
         self.state_slots: torch.Tensor = None     # int32 [S]
         self.rows: torch.Tensor = None            # int32 [R] flat rows whose logits are wanted
+        self.prefill_seqs: torch.Tensor = None    # int32 [P] requests that feed more than one token (prompt portions)
         self.tables: list[torch.Tensor] = []      # per group int32 [S, width]
         lens = [b - a for a, b in zip(host.cu_q, host.cu_q[1:])]
         self.max_q_len = max(lens, default=0)     # which attention kernels a step needs is decided on the host
@@ -207,6 +208,8 @@ class StepRunner:
             if S > len(entries):
                 flat.extend([-1] * (width * (S - len(entries))))
             sections.append(flat)
+        portions = [s for s, e in enumerate(entries) if len(e.tokens) > 1]
+        sections.append(portions)
         # one list, one conversion, one copy into the pinned buffer, one copy to the device
         offsets, packed = [], []
         for sec in sections:
@@ -237,6 +240,7 @@ class StepRunner:
         ctx.token_ids, ctx.positions, ctx.seq_of_token = view(0, T), view(1, T), view(2, T)
         ctx.cu_q, ctx.ctx_lens, ctx.rows, ctx.state_slots = view(3, S + 1), view(4, S), view(5, R), view(6, S)
         ctx.tables = [view(7 + g, S * widths[g]).view(S, widths[g]) for g in range(groups)]
+        ctx.prefill_seqs = view(7 + groups, len(portions))
         return ctx
 
     # ------------------------------------------------------------------ the step
@@ -323,6 +327,7 @@ class StepRunner:
                     flat.extend([-1] * (width - len(t)))
             flat.extend([-1] * (width * extra))
             section(flat)
+        section([])                                                               # no prompt portions
         total = len(packed)
         if self._staging is None or self._staging.numel() < total:
             self._staging = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()

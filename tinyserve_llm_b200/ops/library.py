@@ -179,6 +179,8 @@ class Ops:
             num_seqs = ctx.ctx_lens.shape[0]
             scratch, floats = None, 0
             max_q_len = ctx.max_q_len
+            prefill_seqs = getattr(ctx, "prefill_seqs", None)      # the step runner lists them; a bare context may not
+            num_prefill = prefill_seqs.shape[0] if prefill_seqs is not None else 0
             if (max_q_len > 1 and self.tcgen05_attention and self.lib.ts_attention_tcgen05_supported(
                     c_int(hd), c_int(binding.page_tokens), c_int(nh), c_int(nkv), c_int(window))):
                 # prompt portions on the tcgen05 kernel; requests that feed one token stay with the split-key kernels
@@ -190,7 +192,7 @@ class Ops:
                            c_int(binding.entry_offset // per_entry), c_int(binding.page_tokens), _ptr(binding.block_table),
                            c_int(binding.table_width), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), c_int(num_seqs),
                            c_int(qkv.shape[0]), c_int(max_q_len), c_int(nh), c_int(nkv), c_int(hd), c_float(scale),
-                           c_void_p(self._error_word.data_ptr()), _stream())
+                           _ptr(prefill_seqs), c_int(num_prefill), c_void_p(self._error_word.data_ptr()), _stream())
                 if ctx.min_q_len > 1:
                     return out
                 max_q_len = 1
@@ -207,7 +209,8 @@ class Ops:
                        c_int(binding.num_pages), _ptr(binding.block_table), c_int(binding.table_width),
                        _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), c_int(num_seqs), c_int(max_q_len),
                        c_int(min(ctx.min_q_len, max_q_len)), c_int(ctx.max_ctx_len), c_int(nh), c_int(nkv), c_int(hd),
-                       c_float(scale), c_int(window), _ptr(scratch), c_longlong(floats), _stream())
+                       c_float(scale), c_int(window), _ptr(scratch), c_longlong(floats), _ptr(prefill_seqs),
+                       c_int(num_prefill), _stream())
             if ctx.min_q_len <= 1:
                 self.launches += 1 if max_q_len <= 1 else 2          # decode + combine (+ prefill) in one call
             return out
