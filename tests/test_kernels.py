@@ -351,9 +351,10 @@ def test_skinny_bfloat16_product(ops, m, n, k):
     assert torch.equal(alone[0], ops.linear(x.to(DEV), w.to(DEV), out_dtype=torch.float32).cpu()[0])
 
 
-@pytest.mark.parametrize("m", [1, 8, 20, 40])
+@pytest.mark.parametrize("m", [1, 8, 20, 40, 1500])
 @pytest.mark.parametrize("inter, k", [(176, 64), (500, 192), (8192, 2048), (5, 32)])
 def test_linear_with_swiglu_epilogue(ops, m, inter, k):
+    """Every route: the decode product (up to 32 rows), the library product plus activation, the tcgen05 product (many rows)."""
     x, w = rand((m, k), torch.bfloat16, 7), rand((2 * inter, k), torch.bfloat16, 8, 0.2)
     gate_up = plain.rnd(x.double() @ w.double().T, "bfloat16")
     want = plain.swiglu(gate_up, "bfloat16")
@@ -382,7 +383,7 @@ def test_tcgen05_product_with_swiglu_epilogue(ops, m, inter, k):
     x, w = rand((m, k), torch.bfloat16, 7), rand((2 * inter, k), torch.bfloat16, 8, 0.2)
     gate_up = plain.rnd(x.double() @ w.double().T, "bfloat16")
     want = plain.swiglu(gate_up, "bfloat16")
-    got = ops.linear_swiglu(x.to(DEV), w.to(DEV)).cpu().double()
+    got = ops.gemm_tcgen05(x.to(DEV), w.to(DEV), swiglu=True).cpu().double()
     scale = want.abs().max().item()
     torch.testing.assert_close(got, want, atol=scale * 2 ** -7, rtol=2 ** -6)
     torch.cuda.synchronize()

@@ -114,11 +114,13 @@ struct GemmParams {
     int* error;
 };
 
-template <int EPI, int BN>
+template <int EPI, int BN, int STAGES>
 __global__ void __launch_bounds__(192) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                            const __grid_constant__ CUtensorMap map_b, GemmParams p) {
     constexpr int B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int STAGES = BN == 256 ? 4 : 3;       // narrow tiles: two CTAs share an SM
+    // STAGES: 4 for wide tiles; 3 for narrow ones, of which two CTAs share an SM; 6 for narrow tiles when x has
+    // a single tile of rows: then a CTA does one tile, nothing hides the latency of memory but the depth of
+    // the ring, and the product is bound by the stream of W
     constexpr int OUT_COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;          // output columns per tile
     constexpr int TMEM_COLS = 2 * BN;                                   // two accumulators
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -362,20 +364,25 @@ TS_API int ts_gemm_tcgen05(const void* W, const void* x, void* y, int M, int N, 
     if (make_map(&map_a, x, M, K, ldx, BM)) return 1;
     if (make_map(&map_b, W, N, K, K, out_per_tile)) return 1;
     GemmParams p{y, M, N, K, ldy, inter, out_dtype == TS_F32 ? 1 : 0, error};
-    const int stages = wide ? 4 : 3;
+    const bool deep = !wide && m_tiles == 1;
+    const int stages = wide ? 4 : (deep ? 6 : 3);
     const size_t smem = (size_t)stages * (A_BYTES + bn * BK * 2) + 1024;
-    const int slots = wide ? sms : 2 * sms;         // narrow tiles: half the shared memory and tensor memory each
+    const int slots = wide || deep ? sms : 2 * sms; // narrow tiles: half the shared memory and tensor memory each
     dim3 grid(num_tiles < slots ? num_tiles : slots);
-#define TS_GEMM_LAUNCH(EPI_, BN_)                                                                          \
+#define TS_GEMM_LAUNCH(EPI_, BN_, STAGES_)                                                                 \
     do {                                                                                                   \
-        auto kernel = gemm_tcgen05_kernel<EPI_, BN_>;                                                      \
+        auto kernel = gemm_tcgen05_kernel<EPI_, BN_, STAGES_>;                                             \
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
         TS_CHAINED_CHECK("gemm_tcgen05", launch_chained(kernel, grid, dim3(192), smem, stream, map_a, map_b, p)); \
     } while (0)
     if (epilogue == EPI_SWIGLU) {
-        if (wide) TS_GEMM_LAUNCH(EPI_SWIGLU, 256); else TS_GEMM_LAUNCH(EPI_SWIGLU, 128);
+        if (wide) TS_GEMM_LAUNCH(EPI_SWIGLU, 256, 4);
+        else if (deep) TS_GEMM_LAUNCH(EPI_SWIGLU, 128, 6);
+        else TS_GEMM_LAUNCH(EPI_SWIGLU, 128, 3);
     } else {
-        if (wide) TS_GEMM_LAUNCH(EPI_STORE, 256); else TS_GEMM_LAUNCH(EPI_STORE, 128);
+        if (wide) TS_GEMM_LAUNCH(EPI_STORE, 256, 4);
+        else if (deep) TS_GEMM_LAUNCH(EPI_STORE, 128, 6);
+        else TS_GEMM_LAUNCH(EPI_STORE, 128, 3);
     }
 #undef TS_GEMM_LAUNCH
     return 0;

@@ -47,6 +47,10 @@ class Ops:
         self.set_chaining(os.environ.get("TINYSERVE_B200_CHAINING", "1") != "0")
         # TINYSERVE_B200_PREFILL=mma keeps prompt attention on the mma.sync kernel (the tcgen05 one is the default)
         self.tcgen05_attention = os.environ.get("TINYSERVE_B200_PREFILL", "tcgen05") != "mma"
+        # From this many rows of x the gate/up product runs on the engine's tcgen05 kernel with SwiGLU in its
+        # epilogue (10 to 20 % faster than the library product plus an activation kernel from 1,536 rows on a B200);
+        # below it the library product wins, whose tiles fit a few row tiles better.
+        self.tcgen05_swiglu_min_rows = int(os.environ.get("TINYSERVE_B200_SWIGLU_ROWS", "1408"))
 
     def set_chaining(self, enabled: bool) -> None:
         self.chaining = bool(enabled)
@@ -298,7 +302,7 @@ class Ops:
         if gate_up_weight.shape[0] % 2 or x.shape[1] != gate_up_weight.shape[1]:
             raise KernelError("linear_swiglu: the weight must hold gate and up halves over x's columns")
         if not self._skinny(x, gate_up_weight):
-            if x.dtype == torch.bfloat16 and self.lib.ts_gemm_tcgen05_supported(
+            if x.dtype == torch.bfloat16 and x.shape[0] >= self.tcgen05_swiglu_min_rows and self.lib.ts_gemm_tcgen05_supported(
                     _ptr(gate_up_weight), _ptr(x), c_int(x.shape[0]), c_int(gate_up_weight.shape[0]), c_int(x.shape[1]),
                     c_longlong(x.shape[1])):
                 # tcgen05 product with the activation in its epilogue: the [M, 2I] product never reaches memory
