@@ -233,6 +233,9 @@ def test_random_orders_of_requests_keep_the_contract(seed, kind):
             m.release(seq_id)
             del live[seq_id]
         check_invariants(m, s)
+        # the one-pass count for a batch of single tokens equals the sum of the per-request counts
+        each = [m.pages_needed_to_extend(i, 1) for i in live]
+        assert m.pages_for_one_more_each(list(live)) == [sum(e[g] for e in each) for g in range(len(m.pools))]
     for seq_id in list(live):
         m.release(seq_id)
     check_invariants(m, s)

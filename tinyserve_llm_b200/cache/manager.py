@@ -346,12 +346,33 @@ class CacheManager:
     def can_extend(self, seq_id: int, n: int) -> bool:
         return self.fits(self.pages_needed_to_extend(seq_id, n))
 
-    def extend(self, seq_id: int, tokens: Sequence[int]) -> None:
-        """Reserves slots for the step's tokens of a running request; commit() closes the step."""
+    def pages_for_one_more_each(self, seq_ids: Sequence) -> list[int]:
+        """Per group, the pages that one more token for each of these requests would take: one pass, for large batches."""
+        B = self.page_tokens
+        need = [0] * len(self.pools)
+        seqs = self.seqs
+        for seq_id in seq_ids:
+            seq = seqs[seq_id]
+            reserved = len(seq.tokens)
+            whole = reserved // B + 1
+            inside = reserved % B
+            for g, pool in enumerate(self.pools):
+                table = seq.tables[g]
+                if whole > len(table):
+                    need[g] += whole - len(table)
+                if inside and table and table[-1] >= 0 and pool.refs[table[-1]] > 1:
+                    need[g] += 1                       # the shared last page is copied before the write
+        return need
+
+    def extend(self, seq_id: int, tokens: Sequence[int], checked: bool = False) -> None:
+        """
+        Reserves slots for the step's tokens of a running request; commit() closes the step.
+        `checked`: the caller has made sure the pages are there (pages_for_one_more_each + fits).
+        """
         assert len(tokens) > 0, "a step feeds at least one token"
         seq = self.seqs[seq_id]
-        assert seq.reserved == seq.committed, "the previous step was not committed"
-        if not self.fits(self._pages_to_reserve(seq, len(tokens))):
+        assert len(seq.tokens) == seq.committed, "the previous step was not committed"
+        if not checked and not self.fits(self._pages_to_reserve(seq, len(tokens))):
             raise CacheFull("not enough free pages: check can_extend() first")
         self._reserve(seq, tokens)
 

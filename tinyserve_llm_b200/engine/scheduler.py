@@ -307,19 +307,16 @@ class Scheduler:
         going_on = [s.seq for s in alive if len(s.seq.output_token_ids) + 1 < s.seq.params.max_tokens]
         if not going_on:
             return None
-        needed = [0] * len(self.cache.pools)
-        for seq in going_on:
-            for g, pages in enumerate(self.cache.pages_needed_to_extend(seq.seq_id, 1)):
-                needed[g] += pages
-        if not self.cache.fits(needed):
+        if not self.cache.fits(self.cache.pages_for_one_more_each([seq.seq_id for seq in going_on])):
             return None                          # someone has to give way: decided when the tokens are known
         for s in alive:
             self.cache.commit(s.seq.seq_id, len(s.token_ids))
+        pending = [PENDING_TOKEN]
         ahead = []
         for seq in going_on:
-            self.cache.extend(seq.seq_id, [PENDING_TOKEN])
-            ahead.append(ScheduledSeq(seq, [PENDING_TOKEN], 1))
-            self.counters.decode_tokens += 1
+            self.cache.extend(seq.seq_id, pending, checked=True)
+            ahead.append(ScheduledSeq(seq, pending, 1))
+        self.counters.decode_tokens += len(ahead)
         return ahead
 
     # ------------------------------------------------------------------ after the model ran

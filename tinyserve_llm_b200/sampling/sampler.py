@@ -9,18 +9,41 @@ else is in the batch or on how its prompt was cut into portions.
 
 from __future__ import annotations
 
-import hashlib
-import struct
 from typing import Sequence
 
+import numpy as np
 import torch
+
+_GOLDEN = np.uint64(0x9E3779B97F4A7C15)
+_FIELD_SALT = [np.uint64((0x9E3779B97F4A7C15 * (c + 2)) & 0xFFFFFFFFFFFFFFFF) for c in range(3)]
+_MUL_A = np.uint64(0xBF58476D1CE4E5B9)
+_MUL_B = np.uint64(0x94D049BB133111EB)
+
+
+def _mix(z: np.ndarray) -> np.ndarray:
+    """The finaliser of splitmix64 on an array of uint64 (arithmetic wraps)."""
+    z = (z ^ (z >> np.uint64(30))) * _MUL_A
+    z = (z ^ (z >> np.uint64(27))) * _MUL_B
+    return z ^ (z >> np.uint64(31))
+
+
+def draw_keys(seed: int, draws) -> np.ndarray:
+    """
+    int32 [n, 2]: the two words of the kernel's Philox key for each draw (request id, sample index,
+    output position), a chain of splitmix64 finalisers over the seed and the three fields.  One
+    vectorised pass: a step of hundreds of requests spends microseconds here, not a hash call each.
+    """
+    fields = np.asarray(draws, dtype=np.int64).reshape(-1, 3).astype(np.uint64)
+    h = _mix(np.full(fields.shape[0], seed, dtype=np.int64).astype(np.uint64) + _GOLDEN)
+    for c in range(3):
+        h = _mix(h ^ (fields[:, c] + _FIELD_SALT[c]))
+    return h.view(np.int32).reshape(-1, 2)
 
 
 def draw_key(seed: int, request_id: int, sample_index: int, position: int) -> tuple[int, int]:
     """Two 32-bit words for the kernel's Philox key."""
-    digest = hashlib.blake2b(struct.pack("<qqqq", seed, request_id, sample_index, position), digest_size=8).digest()
-    k0, k1 = struct.unpack("<ii", digest)
-    return k0, k1
+    k0, k1 = draw_keys(seed, [(request_id, sample_index, position)])[0]
+    return int(k0), int(k1)
 
 
 class PendingTokens:
@@ -72,11 +95,11 @@ class Sampler:
             return PendingTokens(None, None, None, 0)
         if rows is not None and list(rows) != list(range(logits.shape[0])):
             logits = logits.index_select(0, torch.tensor(list(rows), dtype=torch.int64, device=logits.device))
-        bits, keys = [], []
-        for d, t in zip(draws, temperatures):
-            bits.append(struct.unpack("<i", struct.pack("<f", t))[0])
-            keys.extend(draw_key(self.seed, *d) if t > 0 else (0, 0))
-        dev = torch.tensor(bits + keys, dtype=torch.int32).to(self.device, non_blocking=True)   # one small copy
+        temps = np.asarray(temperatures, dtype=np.float32)
+        keys = draw_keys(self.seed, draws)
+        keys[temps <= 0] = 0                               # greedy rows draw nothing
+        packed = np.concatenate((temps.view(np.int32), keys.reshape(-1)))
+        dev = torch.from_numpy(packed).to(self.device, non_blocking=True)                         # one small copy
         temps_dev = dev[:count].view(torch.float32)
         keys_dev = dev[count:].view(count, 2)
         tokens = self.ops.sample(logits.contiguous(), temps_dev, keys_dev)
