@@ -301,7 +301,10 @@ class Ops:
         self._check(gate_up_weight, "weight", x.dtype, 2)
         if gate_up_weight.shape[0] % 2 or x.shape[1] != gate_up_weight.shape[1]:
             raise KernelError("linear_swiglu: the weight must hold gate and up halves over x's columns")
-        if not self._skinny(x, gate_up_weight):
+        # the decode product serves up to 8 rows here: from 9 rows on, its CTAs (two or four tiles of x each) no longer
+        # fit the SMs in one wave for a matrix of this many rows, and the library product plus the activation
+        # kernel is faster (18 against 15 us at 16 rows of Llama 3.2 1B's sizes on a B200)
+        if not (self._skinny(x, gate_up_weight) and x.shape[0] <= 8):
             if x.dtype == torch.bfloat16 and x.shape[0] >= self.tcgen05_swiglu_min_rows and self.lib.ts_gemm_tcgen05_supported(
                     _ptr(gate_up_weight), _ptr(x), c_int(x.shape[0]), c_int(gate_up_weight.shape[0]), c_int(x.shape[1]),
                     c_longlong(x.shape[1])):
