@@ -189,3 +189,39 @@ def test_command_line_writes_one_json_record(model_folders, tmp_path):
     assert [c["token_ids"][0] for c in record["completions"]] == \
         [plain.greedy_generate(cfg, tensors, p, 5) for p in ([1, 2, 3, 4], [9, 8, 7])]
     assert record["output_tokens"] == 10 and "output tok/s" in proc.stdout
+
+
+@pytest.mark.parametrize("cuda_graphs", [True, False])
+def test_a_token_fed_on_the_device_gives_the_step_the_host_token_gives(model_folders, cuda_graphs):
+    """`StepEntry.feed`: the step reads its token from a device tensor (the previous step's samples) and equals the step given the same token by the host."""
+    from tinyserve_llm_b200.engine.loading import build_cache, load_model
+    from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
+    model = load_model(model_folders["b"], "float32", "cuda")
+    vocab = TINY_B["vocab_size"]
+    prompts = [ru.random_ids(vocab, n, 70 + n) for n in (5, 40, 17)]
+    nexts = [11, 3, vocab - 1]
+    results = []
+    for fed_on_device in (False, True):
+        _, manager, storage = build_cache(model, PAGE_B, 16, caching=False)
+        runner = StepRunner(model, manager, storage, cuda_graphs=cuda_graphs)
+        for i, p in enumerate(prompts):
+            assert manager.admit(i, p)
+        runner.step([StepEntry(i, p, []) for i, p in enumerate(prompts)])
+        for i, p in enumerate(prompts):
+            manager.commit(i, len(p))
+        for round_ in range(2):                                    # twice: the second decode step replays the captured graph
+            for i in range(3):
+                manager.extend(i, [nexts[i]])
+            if fed_on_device:                                      # samples of "the step before", in another order than the entries
+                device_tokens = torch.tensor([nexts[2], 0, nexts[0], nexts[1]], dtype=torch.int32, device="cuda")
+                entries = [StepEntry(0, (0,), (0,), feed=2), StepEntry(1, (0,), (0,), feed=3), StepEntry(2, (0,), (0,), feed=0)]
+                logits = runner.step(entries, device_tokens)
+            else:
+                logits = runner.step([StepEntry(i, [nexts[i]], [0]) for i in range(3)])
+            results.append(logits.cpu().clone())
+            for i in range(3):
+                manager.commit(i, 1)
+        with pytest.raises(ValueError, match="fed on the device"):
+            manager.extend(0, [1])
+            runner.step([StepEntry(0, (0,), (0,), feed=9)], torch.zeros(2, dtype=torch.int32, device="cuda"))
+    assert torch.equal(results[0], results[2]) and torch.equal(results[1], results[3])
