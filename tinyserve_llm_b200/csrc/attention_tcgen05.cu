@@ -30,8 +30,12 @@ namespace {
 #endif
 constexpr int QROWS = 128, KEYS = TS_FLASH_KEYS, HD = 64;     // queries per CTA, keys per tile
 constexpr int Q_BYTES = QROWS * HD * 2, KV_BYTES = KEYS * HD * 2, STAGE_BYTES = 2 * KV_BYTES;
-constexpr int O_COL = KEYS;                  // S / P at columns 0..KEYS-1, O after them
-constexpr int TMEM_COLS = KEYS + HD <= 128 ? 128 : 256;
+constexpr int O_COL = KEYS;                  // S at columns 0..KEYS-1, O after it, P (bfloat16 pairs) after O
+constexpr int P_COL = KEYS + HD;
+constexpr int TMEM_COLS = 256;
+static_assert(P_COL + KEYS / 2 <= TMEM_COLS, "S, O and P must fit the allocation");
+constexpr int SOFTMAX_WARPS = 8;             // two threads a query row: each takes half of the tile's keys and half of O's dims
+constexpr int PRODUCER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1, THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr long long WAIT_CYCLES = 4000000000ll;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -140,6 +144,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// The two softmax warps of a quadrant meet at a named barrier of their own (ids 1..4; 0 is __syncthreads).
+__device__ __forceinline__ void pair_barrier(int quadrant) {
+    switch (quadrant) {
+        case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+        case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+        case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+        default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+    }
+}
+
 struct FlashParams {
     __nv_bfloat16* out;               // [T, nh * HD]
     const int* block_table;
@@ -154,7 +168,7 @@ struct FlashParams {
     int* error;
 };
 
-__global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(THREADS) prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         FlashParams p) {
@@ -162,6 +176,8 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
     __shared__ __align__(8) uint64_t q_full, kv_full[2], stage_free[2], s_done, p_ready, all_done;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int failed;
+    __shared__ float half_max[2][2][QROWS];          // [tile parity][half][row]: the two threads of a row exchange their maxima
+    __shared__ float half_sum[2][QROWS];             // ... and, at the end, their sums
 
     // blockIdx.x (which varies fastest in the order CTAs are handed out) is the head, blockIdx.y counts the
     // request's tiles from its last: the tile with the most keys of every head starts first, and
@@ -195,12 +211,12 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
             mbar_init(&stage_free[s], 1);
         }
         mbar_init(&s_done, 1);
-        mbar_init(&p_ready, 128);
+        mbar_init(&p_ready, SOFTMAX_WARPS * 32);
         mbar_init(&all_done, 1);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
                      "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -210,7 +226,7 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base_slot;
 
-    if (warp == 4 && lane == 0) {
+    if (warp == PRODUCER_WARP && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
         mbar_expect_tx(&q_full, Q_BYTES);
         tma_load_2d(q_tile, &map_q, &q_full, head * HD, q_begin + row0);
@@ -230,7 +246,7 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
                 tma_load_2d(v_tile + h * (64 * HD * 2), &map_v, &kv_full[s], 0, row);
             }
         }
-    } else if (warp == 5 && lane == 0) {
+    } else if (warp == MMA_WARP && lane == 0) {
         // ---------------------------------------------------------------- MMA issuer
         const uint32_t idesc_s = instr_desc(QROWS, KEYS, false);
         const uint32_t idesc_o = instr_desc(QROWS, HD, true);
@@ -250,29 +266,43 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int k = 0; k < KEYS / 16; ++k)      // O += P V: 16 keys are 8 columns of packed P and 16 rows (2048 bytes) of V
-                umma_ts(tmem + O_COL, tmem + 8 * k, v_desc + 128 * k, idesc_o, (j | k) != 0);
+                umma_ts(tmem + O_COL, tmem + P_COL + 8 * k, v_desc + 128 * k, idesc_o, (j | k) != 0);
             umma_commit(&stage_free[s]);
         }
         if (!ok) failed = 1;
         umma_commit(&all_done);
-    } else if (warp < 4) {
-        // ---------------------------------------------------------------- softmax: thread r owns query row r
-        const int r = threadIdx.x;
+    } else if (warp < SOFTMAX_WARPS) {
+        // ---------------------------------------------------------------- softmax: two threads own query row r
+        // Warp w reads the tensor-memory lanes of quadrant w % 4 (a warp can reach no others); the two
+        // warps of a quadrant split the tile's keys, and O's dims, in halves.  They exchange their
+        // halves' maxima through shared memory once a tile, behind a barrier of their 64 threads.
+        const int quadrant = warp & 3, half = warp >> 2;
+        const int r = quadrant * 32 + lane;
         const int pos = r < rows ? pos0 + r : -1;    // -1: a padding row sees nothing
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        const uint32_t lane_addr = tmem + ((uint32_t)(quadrant * 32) << 16);
+        constexpr int HK = KEYS / 2, HO = HD / 2;    // this thread's keys of a tile, and its dims of O
+        const int col0 = half * HK;
         float m_run = -INFINITY, l_run = 0.f;
         bool ok = true;
         for (int j = 0; j < num_kv; ++j) {
             const int s = j & 1;
             const int key0 = j * KEYS;
-            if (!mbar_wait(&s_done, j & 1, p.error, 15)) { ok = false; break; }
+            // a wait that ran out: the warp (as one) skips the work of this and the later tiles but still meets its
+            // partner at the barrier below and still arrives at p_ready, so that nobody is left waiting for it
+            if (ok && !mbar_wait(&s_done, j & 1, p.error, 15)) ok = false;
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                pair_barrier(quadrant);
+                mbar_arrive(&p_ready);
+                continue;
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const bool masked = key0 + KEYS - 1 > pos0;        // some row of the tile does not see all of these keys
-            // pass 1: the row's maximum over the tile (four running maxima: no long dependent chain).  Reading S
-            // twice from tensor memory measured faster than holding the row in 128 registers.
+            // pass 1: the maximum over this thread's keys (four running maxima: no long dependent chain).  Reading S
+            // twice from tensor memory measured faster than holding the row in registers.
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll 1
-            for (int c = 0; c < KEYS; c += 32) {
+            for (int c = col0; c < col0 + HK; c += 32) {
                 uint32_t v[32];
                 tmem_ld32(lane_addr + c, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -285,15 +315,18 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
                     for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
                 }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            half_max[j & 1][half][r] = mx;
+            pair_barrier(quadrant);
+            mx = fmaxf(mx, half_max[j & 1][half ^ 1][r]);
             const float m_new = fmaxf(m_run, mx * p.scale_log2);
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float corr = fast_exp2(m_run - m_use);
             m_run = m_new;
-            // pass 2: P = exp2(S * scale - m) as bfloat16 pairs, written over S (pair i covers keys 2i, 2i+1)
+            // pass 2: P = exp2(S * scale - m) as bfloat16 pairs into P's own columns (pair i covers keys 2i, 2i+1)
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
-            for (int c = 0; c < KEYS; c += 32) {
+            for (int c = col0; c < col0 + HK; c += 32) {
                 uint32_t v[32], packed[16];
                 tmem_ld32(lane_addr + c, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -308,14 +341,14 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
                     l4[(i >> 1) & 3] += p0 + p1;
                     packed[i >> 1] = pack_bf16(p0, p1);
                 }
-                tmem_st16(lane_addr + (c >> 1), packed);
+                tmem_st16(lane_addr + P_COL + (c >> 1), packed);
             }
             l_run = l_run * corr + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
-            // O of the tiles so far follows the new maximum (its last update has retired: S of this tile came
+            // this thread's dims of O follow the new maximum (O's last update has retired: S of this tile came
             // after it); skipped when no row of the warp moved its maximum
             if (j > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {
 #pragma unroll 1
-                for (int c = 0; c < HD; c += 32) {
+                for (int c = half * HO; c < half * HO + HO; c += 32) {
                     uint32_t v[32];
                     tmem_ld32(lane_addr + O_COL + c, v);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -325,7 +358,7 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
                 }
             }
             // value rows beyond the request's length hold whatever the page held: zero them before they are multiplied
-            if (r < KEYS && key0 + KEYS > ctx && key0 + r >= ctx) {
+            if (half == 0 && r < KEYS && key0 + KEYS > ctx && key0 + r >= ctx) {
                 unsigned char* v_row = kv_tiles + s * STAGE_BYTES + KV_BYTES + r * (HD * 2);
 #pragma unroll
                 for (int i = 0; i < HD * 2; i += 16) *reinterpret_cast<uint4*>(v_row + i) = make_uint4(0, 0, 0, 0);
@@ -336,12 +369,17 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
             mbar_arrive(&p_ready);
         }
         if (ok) ok = mbar_wait(&all_done, 0, p.error, 16);
+        ok = __all_sync(0xffffffffu, ok);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // the row's sum is the two halves' sums (both were kept against the same maxima)
+        half_sum[half][r] = l_run;
+        pair_barrier(quadrant);
+        l_run += half_sum[half ^ 1][r];
         if (ok && !failed) {                         // every thread of the warp takes part in the loads; only real rows store
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             __nv_bfloat16* o = p.out + ((long long)(q_begin + row0 + r) * p.nh + head) * HD;
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 32) {
+            for (int c = half * HO; c < half * HO + HO; c += 32) {
                 uint32_t v[32];
                 tmem_ld32(lane_addr + O_COL + c, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -361,7 +399,7 @@ __global__ void __launch_bounds__(192) prefill_attention_tcgen05_kernel(const __
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
@@ -448,6 +486,6 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
     auto kernel = prefill_attention_tcgen05_kernel;
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(nh, (max_q_len + QROWS - 1) / QROWS, prefill_seqs ? num_prefill_seqs : num_seqs);
-    TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(192), smem, stream, map_q, map_k, map_v, p));
+    TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p));
     return 0;
 }
