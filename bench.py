@@ -233,6 +233,27 @@ def run_ours(args) -> dict:
 
     for i in range(3):
         prefill_once(i)
+    if args.profile_step is not None:
+        if args.profile_step == "prefill":
+            torch.cuda.profiler.start()
+            prefill_once(99)
+            torch.cuda.profiler.stop()
+        else:
+            start_decoding(BATCH, CONTEXT, 64 + 512)
+            entries = []
+            for s in list(llm.scheduler.running):
+                cache.extend(s.seq_id, [s.output_token_ids[-1]])
+                entries.append(StepEntry(s.seq_id, [s.output_token_ids[-1]], [0]))
+            temps = torch.zeros(BATCH, dtype=torch.float32, device=llm.device)
+            keys = torch.zeros((BATCH, 2), dtype=torch.int32, device=llm.device)
+            for _ in range(3):
+                ops.sample(runner.step(entries), temps, keys)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            ops.sample(runner.step(entries), temps, keys)
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        return {"impl": "ours", "profiled": f"one {args.profile_step} step", "config": {"model": model_name, "layers": layers}}
     prefill_ms = statistics.median(prefill_once(10 + i) for i in range(5))
 
     peak, peak_kind = peaks()
@@ -382,6 +403,9 @@ def main() -> int:
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config); 0: all")
     parser.add_argument("--model", choices=sorted(MODELS), default="1b", help="layer sizes: Llama 3.2 1B (default), 3B, 3.1 8B")
+    parser.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
+                        help="no measurement: warm up, then run ONE step of that kind between cudaProfilerStart and "
+                             "cudaProfilerStop (for `ncu --profile-from-start off`), and exit")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (run with --gpus 1)")

@@ -327,8 +327,11 @@ class Ops:
         if temperatures.shape[0] != rows or tuple(keys.shape) != (rows, 2):
             raise KernelError("sample: one temperature and one key pair per logits row are needed")
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+        words = int(self.lib.ts_sample_scratch_words(c_int(rows), c_int(logits.shape[1])))
+        scratch = torch.empty((max(words, 1),), dtype=torch.int32, device=logits.device)    # the chunks' best (value, index)
         self._call("ts_sample", _ptr(logits), c_longlong(logits.shape[1]), _ptr(temperatures), _ptr(keys), _ptr(out),
-                   c_int(rows), c_int(logits.shape[1]), _stream())
+                   c_int(rows), c_int(logits.shape[1]), _ptr(scratch), c_int(words), _stream())
+        self.launches += 1                                   # two kernels in one call
         return out
 
     def copy_page_slots(self, k_pool: torch.Tensor, v_pool: torch.Tensor, src: int, dst: int, num_slots: int) -> None:
