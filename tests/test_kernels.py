@@ -47,10 +47,11 @@ def test_embedding(ops, dtype, hidden, vocab):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden, eps", [(48, 1e-5), (777, 1e-6), (4096, 1e-3), (13000, 1e-5)])
-def test_add_rmsnorm(ops, dtype, hidden, eps):
+@pytest.mark.parametrize("rows", [5, 300])                     # a few rows: a CTA a row; many: rows held in registers
+@pytest.mark.parametrize("hidden, eps", [(48, 1e-5), (777, 1e-6), (4096, 1e-3), (13000, 1e-5), (3072, 1e-5), (8192, 1e-6)])
+def test_add_rmsnorm(ops, dtype, hidden, eps, rows):
     act = act_of(dtype)
-    x, res, w = rand((5, hidden), dtype, 1, 3.0), rand((5, hidden), dtype, 2, 3.0), (1 + rand((hidden,), dtype, 3, 0.3))
+    x, res, w = rand((rows, hidden), dtype, 1, 3.0), rand((rows, hidden), dtype, 2, 3.0), (1 + rand((hidden,), dtype, 3, 0.3))
     w = w.to(dtype)
     want, want_res = plain.add_rms_norm(x.double(), res.double(), w.double(), eps, act)
     xd, rd = x.to(DEV), res.to(DEV)
@@ -68,6 +69,11 @@ def test_add_rmsnorm(ops, dtype, hidden, eps):
     got, _ = ops.add_rmsnorm(xd, rd, w.to(DEV), eps, i32([4, 0, 4]))
     torch.testing.assert_close(got.cpu().double(), want[[4, 0, 4]], **tol(dtype, 4))
     assert torch.equal(xd.cpu(), x) and torch.equal(rd.cpu(), res)
+    if rows > 256:                                             # many chosen rows, some twice, some padding (-1: left alone)
+        pick = [(7 * i) % rows for i in range(290)] + [-1, 3]
+        got, _ = ops.add_rmsnorm(xd, rd, w.to(DEV), eps, i32(pick))
+        keep = [i for i, p in enumerate(pick) if p >= 0]
+        torch.testing.assert_close(got.cpu().double()[keep], want[[pick[i] for i in keep]], **tol(dtype, 4))
 
 
 def test_add_rmsnorm_keeps_a_float32_weight_beside_bfloat16_rows(ops):

@@ -82,12 +82,101 @@ __global__ void add_rmsnorm_kernel(const T* x, const T* residual, const W* __res
     }
 }
 
+// The same for many rows (prompts): a row is held in the registers of TPR threads (up to 8 chunks of
+// 16 bytes each), all its loads are in flight at once, the sum of squares goes through shuffles (and,
+// for rows of more than a warp, once through shared memory), and nothing is staged in shared memory.
+// 256 threads, 256 / TPR rows a CTA.  Needs 16-byte aligned rows and hidden <= TPR * 8 chunks.
+template <typename T, typename W, int TPR>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(const T* x, const T* residual, const W* __restrict__ weight, T* out, T* residual_out,
+                        const int* __restrict__ rows, int num_rows, int hidden, float eps) {
+    constexpr int VN = VecOf<T>::N, MAXC = 8, RPC = 256 / TPR;
+    __shared__ float part[8];
+    const int group = threadIdx.x / TPR, member = threadIdx.x % TPR;
+    const int r = blockIdx.x * RPC + group;
+    const int chunks = hidden / VN;                       // chunk c of the row belongs to thread c % TPR
+    chain_wait();
+    chain_release();
+    const bool live = r < num_rows;
+    const int src = live ? (rows ? rows[r] : r) : -1;
+    float s[MAXC][VN];
+    float acc = 0.f;
+    if (src >= 0) {
+        const T* xr = x + (long long)src * hidden;
+        const T* rr = residual ? residual + (long long)src * hidden : nullptr;
+        uint4 xv[MAXC], rv[MAXC];
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k) {
+            const int c = member + k * TPR;
+            xv[k] = c < chunks ? *reinterpret_cast<const uint4*>(xr + c * VN) : make_uint4(0, 0, 0, 0);
+            rv[k] = (rr && c < chunks) ? *reinterpret_cast<const uint4*>(rr + c * VN) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int k = 0; k < MAXC; ++k) {
+            const T* xe = reinterpret_cast<const T*>(&xv[k]);
+            const T* re = reinterpret_cast<const T*>(&rv[k]);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) {
+                float v = to_float<T>(xe[e]);
+                if (rr) v += to_float<T>(re[e]);
+                s[k][e] = v;
+                acc += v * v;
+            }
+        }
+    }
+    acc = warp_sum(acc);
+    if (TPR > 32) {                                       // a row spans TPR / 32 warps: add their sums in warp order
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        if (lane == 0) part[warp] = acc;
+        __syncthreads();
+        acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < TPR / 32; ++w) acc += part[group * (TPR / 32) + w];
+    }
+    if (src < 0) return;                                  // a padding row, or past the last row
+    const float inv = rsqrtf(acc / (float)hidden + eps);
+    T* outr = out + (long long)r * hidden;
+    T* resr = residual_out ? residual_out + (long long)src * hidden : nullptr;
+#pragma unroll
+    for (int k = 0; k < MAXC; ++k) {
+        const int c = member + k * TPR;
+        if (c >= chunks) continue;
+        uint4 ov, rv;
+        T* oe = reinterpret_cast<T*>(&ov);
+        T* re = reinterpret_cast<T*>(&rv);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+            re[e] = from_float<T>(s[k][e]);
+            oe[e] = from_float<T>(round_to<T>(s[k][e] * inv) * to_float<W>(weight[c * VN + e]));
+        }
+        if (resr) *reinterpret_cast<uint4*>(resr + c * VN) = rv;
+        *reinterpret_cast<uint4*>(outr + c * VN) = ov;
+    }
+}
+
 template <typename T, typename W>
 static int launch(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
                   const int* rows, int num_rows, int hidden, float eps, cudaStream_t stream) {
     const bool vector = hidden % VecOf<T>::N == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                         (residual == nullptr || (uintptr_t)residual % 16 == 0) &&
                         (residual_out == nullptr || (uintptr_t)residual_out % 16 == 0);
+    if (vector && num_rows >= 256) {                       // many rows: rows in registers, several rows a CTA
+        const int chunks = hidden / VecOf<T>::N;
+        const int tpr = chunks <= 32 * 8 ? 32 : (chunks <= 64 * 8 ? 64 : (chunks <= 128 * 8 ? 128 : 0));
+        if (tpr != 0) {
+            const int rows_per_cta = 256 / tpr;
+            const dim3 grid((num_rows + rows_per_cta - 1) / rows_per_cta);
+#define TS_NORM_ROWS(TPR_)                                                                                              \
+    TS_CHAINED_CHECK("add_rmsnorm", launch_chained(add_rmsnorm_rows_kernel<T, W, TPR_>, grid, dim3(256), 0, stream,     \
+                                                   (const T*)x, (const T*)residual, (const W*)weight, (T*)out,          \
+                                                   (T*)residual_out, rows, num_rows, hidden, eps))
+            if (tpr == 32) TS_NORM_ROWS(32);
+            else if (tpr == 64) TS_NORM_ROWS(64);
+            else TS_NORM_ROWS(128);
+#undef TS_NORM_ROWS
+            return 0;
+        }
+    }
     const int per_thread = vector ? VecOf<T>::N : 1;
     int threads = 128;
     while (threads < 512 && threads * per_thread < hidden) threads *= 2;
