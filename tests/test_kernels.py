@@ -396,16 +396,16 @@ def test_tcgen05_product_with_swiglu_epilogue(ops, m, inter, k):
     ops.check_device_errors()
 
 
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("nh, nkv, page", [(8, 2, 64), (32, 8, 256), (5, 5, 128), (3, 1, 64)])
-def test_tcgen05_prompt_attention(ops, nh, nkv, page):
+def test_tcgen05_prompt_attention(ops, nh, nkv, page, hd):
     """
     Prompt portions on the tcgen05 kernel (TMA tiles, S and O in tensor memory): whole prompts of
     several query tiles, a portion over a long cached prefix that ends inside a page, a two-token
     portion, beside requests that decode; against the plain reference and against the mma.sync
     kernel on the same inputs.  Pools are poisoned with NaN: the unwritten tail of a last page must
-    not reach the result.
+    not reach the result.  Head sizes 64 (tiles of 128 keys) and 128 (two sub-tiles of 64 dims, tiles of 64 keys).
     """
-    hd = 64
     q_lens = [300, 1, 130, 2, 128, 1]
     ctx_lens = [300, 700, 1000, 2, 128, 65]
     ctx = make_ctx(q_lens, ctx_lens)

@@ -1,5 +1,7 @@
-// Prefill attention on the fifth-generation tensor cores, head size 64, bfloat16, pages of a multiple
-// of 64 tokens, no window.  A CTA takes 128 consecutive tokens of one request for one query head:
+// Prefill attention on the fifth-generation tensor cores, head sizes 64 and 128, bfloat16, pages of a
+// multiple of 64 tokens, no window.  A CTA takes 128 consecutive tokens of one request for one query head
+// (head size 128: rows lie in shared memory as two sub-tiles of 64 dims, key tiles hold 64 keys, so that
+// two CTAs still fit an SM's shared and tensor memory):
 //
 //   * S = Q K^T for a tile of 128 keys is one tcgen05.mma chain (A = the query tile, B = the key
 //     tile, both brought into 128-byte-swizzled shared memory by TMA straight from the qkv matrix
@@ -28,12 +30,21 @@ namespace {
 #ifndef TS_FLASH_KEYS
 #define TS_FLASH_KEYS 128
 #endif
-constexpr int QROWS = 128, KEYS = TS_FLASH_KEYS, HD = 64;     // queries per CTA, keys per tile
-constexpr int Q_BYTES = QROWS * HD * 2, KV_BYTES = KEYS * HD * 2, STAGE_BYTES = 2 * KV_BYTES;
-constexpr int O_COL = KEYS;                  // S at columns 0..KEYS-1, O after it, P (bfloat16 pairs) after O
-constexpr int P_COL = KEYS + HD;
+constexpr int QROWS = 128;                   // queries per CTA
 constexpr int TMEM_COLS = 256;
-static_assert(P_COL + KEYS / 2 <= TMEM_COLS, "S, O and P must fit the allocation");
+// Sizes that follow from the head size.  A tile row of more than 64 dims lies in shared memory as
+// sub-tiles of 64 dims (128 bytes, the widest row the 128-byte swizzle takes), one after the other.
+template <int HD>
+struct Shape {
+    static constexpr int KEYS = HD == 64 ? TS_FLASH_KEYS : 64;     // keys per tile: two CTAs must fit an SM
+    static constexpr int SUBS = HD / 64;                           // sub-tiles of 64 dims
+    static constexpr int SUB_Q = QROWS * 128, SUB_KV = KEYS * 128; // bytes of a sub-tile
+    static constexpr int Q_BYTES = QROWS * HD * 2, KV_BYTES = KEYS * HD * 2, STAGE_BYTES = 2 * KV_BYTES;
+    static constexpr int O_COL = KEYS;       // S at columns 0..KEYS-1, O after it, P (bfloat16 pairs) after O
+    static constexpr int P_COL = KEYS + HD;
+    static_assert(HD == 64 || HD == 128, "head sizes 64 and 128");
+    static_assert(P_COL + KEYS / 2 <= TMEM_COLS, "S, O and P must fit the allocation");
+};
 constexpr int SOFTMAX_WARPS = 8;             // two threads a query row: each takes half of the tile's keys and half of O's dims
 constexpr int PRODUCER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1, THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr long long WAIT_CYCLES = 4000000000ll;
@@ -168,10 +179,14 @@ struct FlashParams {
     int* error;
 };
 
+template <int HD>
 __global__ void __launch_bounds__(THREADS) prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         FlashParams p) {
+    using S_ = Shape<HD>;
+    constexpr int KEYS = S_::KEYS, SUBS = S_::SUBS, SUB_Q = S_::SUB_Q, SUB_KV = S_::SUB_KV, Q_BYTES = S_::Q_BYTES,
+                  KV_BYTES = S_::KV_BYTES, STAGE_BYTES = S_::STAGE_BYTES, O_COL = S_::O_COL, P_COL = S_::P_COL;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t q_full, kv_full[2], stage_free[2], s_done, p_ready, all_done;
     __shared__ uint32_t tmem_base_slot;
@@ -184,7 +199,6 @@ __global__ void __launch_bounds__(THREADS) prefill_attention_tcgen05_kernel(cons
     // the short ones fill the SMs as the long ones finish.
     const int seq = p.prefill_seqs ? p.prefill_seqs[blockIdx.z] : (int)blockIdx.z, head = blockIdx.x;
     chain_wait();                                    // q, k and v of the step come from kernels ahead on the stream
-    chain_release();
     const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
     if (q_len <= 1) return;                          // decode rows go to the split-key kernels
     const int tiles = (q_len + QROWS - 1) / QROWS;
@@ -225,11 +239,15 @@ __global__ void __launch_bounds__(THREADS) prefill_attention_tcgen05_kernel(cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = tmem_base_slot;
+    // Dependents are let in only now that this CTA holds its tensor memory: a kernel behind this one that
+    // allocates tensor memory before it waits for this grid could otherwise starve a CTA of this grid.
+    chain_release();
 
     if (warp == PRODUCER_WARP && lane == 0) {
         // ---------------------------------------------------------------- TMA producer
         mbar_expect_tx(&q_full, Q_BYTES);
-        tma_load_2d(q_tile, &map_q, &q_full, head * HD, q_begin + row0);
+#pragma unroll
+        for (int h = 0; h < SUBS; ++h) tma_load_2d(q_tile + h * SUB_Q, &map_q, &q_full, head * HD + h * 64, q_begin + row0);
         for (int j = 0; j < num_kv; ++j) {
             const int s = j & 1;
             if (!mbar_wait(&stage_free[s], ((j >> 1) & 1) ^ 1, p.error, 11)) { failed = 1; break; }
@@ -237,36 +255,44 @@ __global__ void __launch_bounds__(THREADS) prefill_attention_tcgen05_kernel(cons
             unsigned char* v_tile = k_tile + KV_BYTES;
             mbar_expect_tx(&kv_full[s], STAGE_BYTES);
 #pragma unroll
-            for (int h = 0; h < KEYS / 64; ++h) {    // boxes of 64 keys: a box never crosses a page
-                const int key = j * KEYS + h * 64;
+            for (int b = 0; b < KEYS / 64; ++b) {    // boxes of 64 keys x 64 dims: a box never crosses a page
+                const int key = j * KEYS + b * 64;
                 int page = table[min(key / p.page_tokens, p.table_width - 1)];
                 if (page < 0 || page >= p.num_pages) page = 0;     // given back or beyond the request: masked anyway
                 const int row = ((page * p.entries + p.entry) * p.nkv + kvh) * p.page_tokens + key % p.page_tokens;
-                tma_load_2d(k_tile + h * (64 * HD * 2), &map_k, &kv_full[s], 0, row);
-                tma_load_2d(v_tile + h * (64 * HD * 2), &map_v, &kv_full[s], 0, row);
+#pragma unroll
+                for (int h = 0; h < SUBS; ++h) {
+                    tma_load_2d(k_tile + h * SUB_KV + b * (64 * 128), &map_k, &kv_full[s], h * 64, row);
+                    tma_load_2d(v_tile + h * SUB_KV + b * (64 * 128), &map_v, &kv_full[s], h * 64, row);
+                }
             }
         }
     } else if (warp == MMA_WARP && lane == 0) {
         // ---------------------------------------------------------------- MMA issuer
         const uint32_t idesc_s = instr_desc(QROWS, KEYS, false);
-        const uint32_t idesc_o = instr_desc(QROWS, HD, true);
+        const uint32_t idesc_o = instr_desc(QROWS, 64, true);        // O in column blocks of 64 dims, one per sub-tile of V
         bool ok = mbar_wait(&q_full, 0, p.error, 12);
-        const uint64_t q_desc = smem_desc(q_tile);
         for (int j = 0; j < num_kv && ok; ++j) {
             const int s = j & 1;
             if (!mbar_wait(&kv_full[s], (j >> 1) & 1, p.error, 13)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t k_desc = smem_desc(kv_tiles + s * STAGE_BYTES);
-            const uint64_t v_desc = smem_desc(kv_tiles + s * STAGE_BYTES + KV_BYTES);
 #pragma unroll
-            for (int k = 0; k < HD / 16; ++k)        // S = Q K^T; the tensor pipe runs the chains in order, after O += P V of the tile before
-                umma_ss(tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_s, k != 0);
+            for (int h = 0; h < SUBS; ++h) {         // S = Q K^T; the tensor pipe runs the chains in order, after O += P V of the tile before
+                const uint64_t q_desc = smem_desc(q_tile + h * SUB_Q);
+                const uint64_t k_desc = smem_desc(kv_tiles + s * STAGE_BYTES + h * SUB_KV);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) umma_ss(tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_s, (h | k) != 0);
+            }
             umma_commit(&s_done);
             if (!mbar_wait(&p_ready, j & 1, p.error, 14)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int k = 0; k < KEYS / 16; ++k)      // O += P V: 16 keys are 8 columns of packed P and 16 rows (2048 bytes) of V
-                umma_ts(tmem + O_COL, tmem + P_COL + 8 * k, v_desc + 128 * k, idesc_o, (j | k) != 0);
+            for (int h = 0; h < SUBS; ++h) {         // O += P V: 16 keys are 8 columns of packed P and 16 rows (2048 bytes) of a V sub-tile
+                const uint64_t v_desc = smem_desc(kv_tiles + s * STAGE_BYTES + KV_BYTES + h * SUB_KV);
+#pragma unroll
+                for (int k = 0; k < KEYS / 16; ++k)
+                    umma_ts(tmem + O_COL + 64 * h, tmem + P_COL + 8 * k, v_desc + 128 * k, idesc_o, (j | k) != 0);
+            }
             umma_commit(&stage_free[s]);
         }
         if (!ok) failed = 1;
@@ -359,9 +385,12 @@ __global__ void __launch_bounds__(THREADS) prefill_attention_tcgen05_kernel(cons
             }
             // value rows beyond the request's length hold whatever the page held: zero them before they are multiplied
             if (half == 0 && r < KEYS && key0 + KEYS > ctx && key0 + r >= ctx) {
-                unsigned char* v_row = kv_tiles + s * STAGE_BYTES + KV_BYTES + r * (HD * 2);
 #pragma unroll
-                for (int i = 0; i < HD * 2; i += 16) *reinterpret_cast<uint4*>(v_row + i) = make_uint4(0, 0, 0, 0);
+                for (int h = 0; h < SUBS; ++h) {
+                    unsigned char* v_row = kv_tiles + s * STAGE_BYTES + KV_BYTES + h * SUB_KV + r * 128;
+#pragma unroll
+                    for (int i = 0; i < 128; i += 16) *reinterpret_cast<uint4*>(v_row + i) = make_uint4(0, 0, 0, 0);
+                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -439,7 +468,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
 }  // namespace
 
 TS_API int ts_attention_tcgen05_supported(int hd, int page_tokens, int nh, int nkv, int window) {
-    return hd == HD && page_tokens % 64 == 0 && nkv > 0 && nh % nkv == 0 && window == 0;
+    return (hd == 64 || hd == 128) && page_tokens % 64 == 0 && nkv > 0 && nh % nkv == 0 && window == 0;
 }
 
 // Prompt portions (requests that feed more than one token) of a step; requests that feed one token
@@ -465,8 +494,8 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
     const long long row_width = (long long)(nh + 2 * nkv) * hd;
     CUtensorMap map_q, map_k, map_v;
     if (make_map(&map_q, qkv, num_tokens, row_width, row_width, QROWS)) return 1;
-    if (make_map(&map_k, k_pool, pool_rows, HD, HD, 64)) return 1;
-    if (make_map(&map_v, v_pool, pool_rows, HD, HD, 64)) return 1;
+    if (make_map(&map_k, k_pool, pool_rows, hd, hd, 64)) return 1;
+    if (make_map(&map_v, v_pool, pool_rows, hd, hd, 64)) return 1;
     FlashParams p;
     p.out = (__nv_bfloat16*)out;
     p.block_table = block_table;
@@ -482,10 +511,17 @@ TS_API int ts_prefill_attention_tcgen05(const void* qkv, void* out, const void* 
     p.entry = entry;
     p.scale_log2 = scale * LOG2E;
     p.error = error;
-    const size_t smem = (size_t)Q_BYTES + 2 * STAGE_BYTES + 1024;
-    auto kernel = prefill_attention_tcgen05_kernel;
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(nh, (max_q_len + QROWS - 1) / QROWS, prefill_seqs ? num_prefill_seqs : num_seqs);
-    TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p));
+    if (hd == 64) {
+        const size_t smem = (size_t)Shape<64>::Q_BYTES + 2 * Shape<64>::STAGE_BYTES + 1024;
+        auto kernel = prefill_attention_tcgen05_kernel<64>;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p));
+    } else {
+        const size_t smem = (size_t)Shape<128>::Q_BYTES + 2 * Shape<128>::STAGE_BYTES + 1024;
+        auto kernel = prefill_attention_tcgen05_kernel<128>;
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        TS_CHAINED_CHECK("attention_tcgen05", launch_chained(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, p));
+    }
     return 0;
 }
