@@ -265,8 +265,6 @@ int dispatch_m(const void* W, const void* x, void* y, int M, int N, int K, long 
     return launch<4, WARPS, EPI, OUT, (WARPS > 8 ? 2 : UNROLL), 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
 }
 
-int g_warps_override = 0;       // tuning aid: 4, 8 or 16 forces plain 16-row tiles with that many warps; 0: the rules below
-
 // How a product is cut into CTAs, chosen from N and K only (never from the rows of x).  Measured on
 // a B200 with Llama 3.2 1B shapes (16 different weights in a row inside a CUDA graph, so nothing
 // stays in L2): the aim is one wave of CTAs that covers all 148 SMs.
@@ -279,9 +277,6 @@ int dispatch_warps(const void* W, const void* x, void* y, int M, int N, int K, l
                    cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
     const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
     const int kblocks = K / 32;
-    if (g_warps_override == 4) return dispatch_m<4, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
-    if (g_warps_override == 8) return dispatch_m<8, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
-    if (g_warps_override == 16) return dispatch_m<16, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
     if (tiles > 296 || kblocks < 32)
         return dispatch_m<4, EPI, OUT, 2, 7>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
     if (tiles > 148) return dispatch_m<8, EPI, OUT, 4, 2>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
@@ -291,8 +286,6 @@ int dispatch_warps(const void* W, const void* x, void* y, int M, int N, int K, l
 }  // namespace
 
 TS_API int ts_skinny_linear_max_rows() { return 32; }
-
-TS_API void ts_skinny_linear_force_warps(int warps) { g_warps_override = warps; }
 
 // y[M, N] = x[M, K] . W[N, K]^T (epilogue 0), or y[M, N/2] = swiglu of it with W = [gate rows | up rows]
 // (epilogue 1).  out_dtype: TS_BF16 or TS_F32.

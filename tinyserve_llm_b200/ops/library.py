@@ -236,7 +236,10 @@ class Ops:
         return out
 
     def linear(self, x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-        """x [M, K] . weight[N, K]^T.  float32: the engine's FFMA kernel.  bfloat16: the library product."""
+        """
+        x [M, K] . weight[N, K]^T.  float32: the engine's FFMA kernel.  bfloat16: up to 32 rows of x on
+        the engine's weight-streaming kernel, more on the library product (cuBLAS through torch.mm).
+        """
         self._check(x, "x", tuple(_DTYPE_CODE), 2)
         self._check(weight, "weight", x.dtype, 2)
         if x.shape[1] != weight.shape[1]:
