@@ -436,3 +436,26 @@ def test_tcgen05_prompt_attention(ops, nh, nkv, page, hd):
     finally:
         ops.tcgen05_attention = True
     torch.testing.assert_close(got, legacy, **tol(torch.bfloat16, 2))
+
+
+def test_environment_switches(ops, monkeypatch):
+    """The library's switches are read when it is loaded; serialised launches give the same bits as chained ones."""
+    from tinyserve_llm_b200.ops.library import Ops
+    monkeypatch.setenv("TINYSERVE_B200_CHAINING", "0")
+    monkeypatch.setenv("TINYSERVE_B200_PREFILL", "mma")
+    monkeypatch.setenv("TINYSERVE_B200_SWIGLU_ROWS", "77")
+    plain_launches = Ops(ops.lib_path)
+    assert not plain_launches.chaining and not plain_launches.tcgen05_attention and plain_launches.tcgen05_swiglu_min_rows == 77
+    x, res = rand((8, 256), torch.bfloat16, 1).to(DEV), rand((8, 256), torch.bfloat16, 2).to(DEV)
+    w, norm_w = rand((512, 256), torch.bfloat16, 3, 0.1).to(DEV), (1 + rand((256,), torch.bfloat16, 4, 0.2)).to(DEV)
+
+    def chain(o):
+        h, _ = o.add_rmsnorm(x.clone(), res.clone(), norm_w, 1e-5)
+        return o.linear_swiglu(h, w)
+
+    try:
+        serial = chain(plain_launches)
+    finally:
+        ops.set_chaining(True)                     # the flag lives in the shared library: hand it back as it was
+    assert ops.chaining and ops.tcgen05_attention
+    assert torch.equal(serial, chain(ops))
