@@ -331,12 +331,26 @@ def test_run_ahead_launches_decode_steps_before_the_samples_are_booked():
     assert len(w.batches) == 9 and w.cache.stats().pages_in_use == 0
 
 
-def test_run_ahead_needs_an_empty_queue_and_every_running_sequence_in_the_step():
+def test_run_ahead_needs_a_queue_that_cannot_be_served_and_every_running_sequence_in_the_step():
     w = World(run_ahead=True, max_num_seqs=1)
     w.add([1, 2, 3], max_tokens=4)
     w.add([4, 5, 6], max_tokens=4)                 # waits for the sequence cap
-    w.run_all()
-    assert w.launched_ahead == 3                   # only the second request's decodes, once nothing waits
+    done = w.run_all()
+    # with the cap full nothing waiting could join the next step, so the first request runs ahead as well: each
+    # request has its three decode steps launched ahead (nothing is launched behind the step that samples a
+    # request's last token: its place is free after that one)
+    assert w.launched_ahead == 6
+    assert _outputs(done, 0) == [reference_output([1, 2, 3], 4)] and _outputs(done, 1) == [reference_output([4, 5, 6], 4)]
+
+    w = World(run_ahead=True, max_num_seqs=3)
+    w.add([1, 2, 3], max_tokens=4)
+    w.step()
+    w.add([4, 5, 6], max_tokens=4)                 # waits only because it came between steps: the cap has room
+    before = w.launched_ahead
+    w.step()                                       # books the step launched ahead before it arrived
+    assert w.launched_ahead == before              # no running ahead while a waiting request could be admitted
+    w.step()                                       # admits it beside the first one's decode
+    assert len(w.scheduler.running) == 2 and w.launched_ahead == before + 1
 
     w = World(run_ahead=True, prefill_chunk=2)
     w.add([1, 2, 3, 4, 5], max_tokens=3)

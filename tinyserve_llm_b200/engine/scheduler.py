@@ -23,8 +23,9 @@ and the step is built again; a step that is empty with nothing running raises in
 Running ahead (new here).  While a decode step is still on the device, `schedule_ahead` may decide
 the step after it: every running sequence feeds the token it is about to sample, which the engine
 passes from step to step on the device.  It does so only where the decision does not depend on
-those tokens: nothing waits, everything running is in the step and samples one token, and the pages
-for one more token each are free.  A sequence that reaches `max_tokens` in the step under way is
+those tokens: nothing waits (or the sequence cap is full and stays full, so that nothing waiting could be
+admitted), everything running is in the step and samples one token, and the pages for one more token
+each are free.  A sequence that reaches `max_tokens` in the step under way is
 left out.  The one thing unknown is an end-of-sequence token: a sequence that samples one finishes
 as usual, its pages are released, and its share of the step launched ahead is thrown away.
 """
@@ -298,14 +299,17 @@ class Scheduler:
         tokens are known, and whatever reads their keys is launched after it), each continuing
         sequence reserves one slot with PENDING_TOKEN as its token, and `postprocess` is told so.
         """
-        if self.waiting:
-            return None
         alive = [s for s in under_way if s.seq.status is SequenceStatus.RUNNING]
         if any(s.num_samples != 1 for s in alive) or {s.seq.seq_id for s in alive} != {s.seq_id for s in self.running}:
             return None
         # the step under way produces output number len(outputs) + 1
         going_on = [s.seq for s in alive if len(s.seq.output_token_ids) + 1 < s.seq.params.max_tokens]
         if not going_on:
+            return None
+        # Requests that wait rule the step out unless none of them could be admitted into it anyway: the
+        # sequence cap is full and stays full (nobody reaches max_tokens in the step under way).  A request
+        # that ends on an end-of-sequence token then hands its place on one step later than it would have.
+        if self.waiting and (len(going_on) < len(alive) or len(self.running) < self.config.max_num_seqs):
             return None
         if not self.cache.fits(self.cache.pages_for_one_more_each([seq.seq_id for seq in going_on])):
             return None                          # someone has to give way: decided when the tokens are known
