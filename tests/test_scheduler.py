@@ -404,3 +404,21 @@ def test_end_of_sequence_under_a_step_launched_ahead():
     a = w.add(prompt, max_tokens=12)
     done = w.run_all()
     assert _outputs(done, a) == [want] and w.dropped == 1 and w.cache.stats().pages_in_use == 0
+
+
+def test_run_ahead_while_requests_wait_for_pages():
+    """The queue waits for pages, not for a sequence slot: steps are launched ahead once an admission pass has found room for none."""
+    w = World(run_ahead=True, pages=6, page_tokens=4, caching=False, max_num_seqs=8)
+    prompts = [[1, 2, 3, 4, 5, 6, 7], [8, 9, 10, 11, 12, 13, 14], [15, 16, 17, 18, 19, 20, 21]]
+    rids = [w.add(p, max_tokens=5) for p in prompts]          # three pages each at full length: the pool holds two of them
+    done = {}
+    saw_ahead_with_queue = False
+    while w.scheduler.has_unfinished():
+        before = w.launched_ahead
+        done.update({o.request_id: o for o in w.step()})
+        if w.launched_ahead > before and w.scheduler.waiting:
+            saw_ahead_with_queue = True
+    assert saw_ahead_with_queue
+    for rid, p in zip(rids, prompts):
+        assert _outputs(done, rid) == [reference_output(p, 5)]
+    assert w.cache.stats().pages_in_use == 0

@@ -23,9 +23,9 @@ and the step is built again; a step that is empty with nothing running raises in
 Running ahead (new here).  While a decode step is still on the device, `schedule_ahead` may decide
 the step after it: every running sequence feeds the token it is about to sample, which the engine
 passes from step to step on the device.  It does so only where the decision does not depend on
-those tokens: nothing waits (or the sequence cap is full and stays full, so that nothing waiting could be
-admitted), everything running is in the step and samples one token, and the pages for one more token
-each are free.  A sequence that reaches `max_tokens` in the step under way is
+those tokens: nothing waits (or nothing waiting could be admitted: the sequence cap is full, or the last
+admission pass found room for none and nothing has made room since), everything running is in the step
+and samples one token, and the pages for one more token each are free.  A sequence that reaches `max_tokens` in the step under way is
 left out.  The one thing unknown is an end-of-sequence token: a sequence that samples one finishes
 as usual, its pages are released, and its share of the step launched ahead is thrown away.
 """
@@ -104,6 +104,11 @@ class Scheduler:
         self._seq_ids = itertools.count()
         self._request_ids = itertools.count()
         self.counters = SchedulerStats()
+        # True from an admission pass that found room for none of the waiting requests until something that
+        # could make room happens (a request arrives, ends or is preempted, a window gives pages back):
+        # pages are only taken meanwhile, so the pass would come out the same
+        self._nothing_admissible = False
+        self._window_releases_seen = 0
 
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
@@ -131,6 +136,7 @@ class Scheduler:
         seq = Sequence(next(self._seq_ids), request_id, tuple(prompt_token_ids), params, arrival_time)
         self.groups[request_id] = [seq]
         self.waiting.append(seq)
+        self._nothing_admissible = False
         return request_id
 
     # ------------------------------------------------------------------ ranking
@@ -242,6 +248,7 @@ class Scheduler:
         return seq.params.n if (seq.params.n > 1 and not seq.output_token_ids) else 1
 
     def _preempt(self, seq: Sequence) -> None:
+        self._nothing_admissible = False
         self.cache.release(seq.seq_id)
         seq.status = SequenceStatus.WAITING
         seq.num_preemptions += 1
@@ -250,6 +257,7 @@ class Scheduler:
 
     def _admit(self, now: float, budget: int) -> list[ScheduledSeq]:
         admitted: list[ScheduledSeq] = []
+        evaluated = budget > 0 and bool(self.waiting)
         owed_forks = 0                                   # forks of groups admitted earlier in this step
         for seq, cost, hit in self._ranked_waiting(now):
             if budget <= 0:
@@ -289,6 +297,8 @@ class Scheduler:
         if admitted:
             chosen = {s.seq.seq_id for s in admitted}
             self.waiting = [s for s in self.waiting if s.seq_id not in chosen]
+        self._nothing_admissible = evaluated and not admitted
+        self._window_releases_seen = self.cache.counters.window_releases
         return admitted
 
     # ------------------------------------------------------------------ the step after the one under way
@@ -306,11 +316,16 @@ class Scheduler:
         going_on = [s.seq for s in alive if len(s.seq.output_token_ids) + 1 < s.seq.params.max_tokens]
         if not going_on:
             return None
-        # Requests that wait rule the step out unless none of them could be admitted into it anyway: the
-        # sequence cap is full and stays full (nobody reaches max_tokens in the step under way).  A request
-        # that ends on an end-of-sequence token then hands its place on one step later than it would have.
-        if self.waiting and (len(going_on) < len(alive) or len(self.running) < self.config.max_num_seqs):
-            return None
+        # Requests that wait rule the step out unless none of them could be admitted into it anyway: nobody
+        # reaches max_tokens in the step under way, and either the sequence cap is full or the last admission
+        # pass found room for none of them and nothing has made room since.  A request that ends on an
+        # end-of-sequence token then hands its place on one step later than it would have.
+        if self.waiting:
+            if len(going_on) < len(alive):
+                return None
+            blocked = self._nothing_admissible and self._window_releases_seen == self.cache.counters.window_releases
+            if not blocked and len(self.running) < self.config.max_num_seqs:
+                return None
         if not self.cache.fits(self.cache.pages_for_one_more_each([seq.seq_id for seq in going_on])):
             return None                          # someone has to give way: decided when the tokens are known
         for s in alive:
@@ -375,6 +390,7 @@ class Scheduler:
         if finished:
             done = {s.seq_id for s in finished}
             self.running = [s for s in self.running if s.seq_id not in done]
+            self._nothing_admissible = False
         outputs = []
         for request_id in dict.fromkeys(s.request_id for s in finished):
             group = self.groups[request_id]
