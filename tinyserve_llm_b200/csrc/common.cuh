@@ -65,19 +65,16 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // Sum over the block in a fixed order (lane tree, then warps in index order): every thread gets it.
-__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+// One barrier: every thread adds up the warps' sums itself, in the same order.  `scratch` must not be
+// in use by other threads when the call begins.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
     v = warp_sum(v);
-    __syncthreads();
     if (lane == 0) scratch[warp] = v;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float t = 0.f;
-        for (int w = 0; w < nwarps; ++w) t += scratch[w];
-        scratch[32] = t;
-    }
-    __syncthreads();
-    return scratch[32];
+    float t = 0.f;
+    for (int w = 0; w < nwarps; ++w) t += scratch[w];
+    return t;
 }
 
 // Programmatic dependent launch.  A kernel launched through launch_chained() may start while the
