@@ -225,3 +225,23 @@ def test_a_token_fed_on_the_device_gives_the_step_the_host_token_gives(model_fol
             manager.extend(0, [1])
             runner.step([StepEntry(0, (0,), (0,), feed=9)], torch.zeros(2, dtype=torch.int32, device="cuda"))
     assert torch.equal(results[0], results[2]) and torch.equal(results[1], results[3])
+
+
+def test_multi_turn_replay_reuses_histories_and_changes_no_token(model_folders, tmp_path):
+    """The multi-turn replay runner: with the prefix cache on, later turns prefill only what is new; the replies are the same."""
+    from tinyserve_llm_b200.cli import multiturn
+    results = {}
+    for caching in ("on", "off"):
+        out = tmp_path / f"{caching}.json"
+        code = multiturn.main(["--model", model_folders["b"], "--conversations", "6", "--turns", "3,4", "--user-tokens", "20,60",
+                               "--reply-tokens", "4,9", "--rho", "0.5", "--caching", caching, "--temperature", "0",
+                               "--dtype", "float32", "--block-size", str(PAGE_B), "--max-model-len", "400",
+                               "--max-num-seqs", "4", "--max-num-batched-tokens", "512", "--out", str(out)])
+        assert code == 0
+        results[caching] = json.loads(out.read_text())
+    on, off = results["on"], results["off"]
+    assert on["final_history_digests"] == off["final_history_digests"]
+    assert off["summary"]["prefill_tokens"] == off["summary"]["prompt_tokens"] - off["scheduler_stats"]["cached_tokens"]
+    assert on["summary"]["prefill_tokens"] < 0.7 * off["summary"]["prefill_tokens"]
+    assert on["summary"]["cached_tokens"] > 0 and on["conversations"] == 6 and len(on["waves"]) >= 3
+    assert abs(on["rho"] - 0.5) < 0.2

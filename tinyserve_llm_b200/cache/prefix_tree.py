@@ -1,6 +1,7 @@
 """
-Prefix index over published cache pages: a tree with one node per page, and under every node a
-token trie over its children, so that a new prompt reuses cached keys and values token by token.
+Prefix index over published cache pages: a tree with one node per page, and under every node an
+index of its children by their leading tokens, so that a new prompt reuses cached keys and values
+token by token.
 
 Behaviour follows tinyserve-llm's page tree (kvcache/page_tree.py:43-128, kvcache/trie.py:28-69):
 a walk matches whole pages by their exact token tuple, then asks the last node's trie for the
@@ -15,52 +16,61 @@ from dataclasses import dataclass, field
 from typing import Iterable, Sequence
 
 
-class _TrieNode:
-    __slots__ = ("next", "pages")
-
-    def __init__(self) -> None:
-        self.next: dict[int, _TrieNode] = {}
-        self.pages: set[PageNode] = set()      # child pages whose tokens run through this node
+def _common_prefix(a: tuple, b: tuple) -> int:
+    """Length of the longest common prefix of two tuples; the comparisons run at C speed on slices."""
+    n = min(len(a), len(b))
+    if a[:n] == b[:n]:
+        return n
+    lo, hi = 0, n                              # a[:lo] == b[:lo] and a[:hi] != b[:hi]
+    while hi - lo > 1:
+        mid = (lo + hi) // 2
+        if a[lo:mid] == b[lo:mid]:
+            lo = mid
+        else:
+            hi = mid
+    return lo
 
 
 class TokenTrie:
-    """Children of one page, indexed by their leading tokens."""
+    """
+    Children of one page, indexed by their leading tokens.  It answers what a trie over the
+    children's tokens answers (kvcache/trie.py:28-69 of the reference), but keeps no node per
+    token: a child is filed under its first token with its token tuple, and the longest shared run
+    is found by comparing tuples when it is asked for.  Publishing a page then costs one dictionary
+    entry instead of one object per token.
+    """
 
-    __slots__ = ("root",)
+    __slots__ = ("by_first",)
 
     def __init__(self) -> None:
-        self.root = _TrieNode()
+        self.by_first: dict[int, dict[object, tuple[int, ...]]] = {}
 
     def add(self, page: "PageNode", tokens: Sequence[int]) -> None:
-        """Index `page` under `tokens`; adding a longer run for the same page extends its path."""
-        node = self.root
-        for tok in tokens:
-            nxt = node.next.get(tok)
-            if nxt is None:
-                nxt = node.next[tok] = _TrieNode()
-            nxt.pages.add(page)
-            node = nxt
+        """Index `page` under `tokens`; adding a longer run for the same page replaces the shorter one."""
+        tokens = tuple(tokens)
+        self.by_first.setdefault(tokens[0], {})[page] = tokens
 
     def discard(self, page: "PageNode", tokens: Sequence[int]) -> None:
-        """Remove `page`'s path, keeping what other pages still run through."""
-        node = self.root
-        for tok in tokens:
-            nxt = node.next[tok]
-            nxt.pages.discard(page)
-            if not nxt.pages:
-                del node.next[tok]           # nothing else passes here, so nothing below does either
-                return
-            node = nxt
+        """Remove `page`, which was added under `tokens` (or under a run `tokens` extends)."""
+        bucket = self.by_first[tokens[0]]
+        del bucket[page]
+        if not bucket:
+            del self.by_first[tokens[0]]
 
     def longest_run(self, tokens: Sequence[int]) -> tuple[int, set["PageNode"]]:
         """(number of leading tokens matched, the children that share that run; read-only)."""
-        node, depth = self.root, 0
-        for tok in tokens:
-            nxt = node.next.get(tok)
-            if nxt is None:
-                break
-            node, depth = nxt, depth + 1
-        return depth, node.pages
+        tokens = tuple(tokens)
+        bucket = self.by_first.get(tokens[0]) if tokens else None
+        if not bucket:
+            return 0, set()
+        best, sharing = 0, set()
+        for page, recorded in bucket.items():
+            depth = _common_prefix(tokens, recorded)
+            if depth > best:
+                best, sharing = depth, {page}
+            elif depth == best:
+                sharing.add(page)
+        return best, sharing
 
 
 @dataclass(eq=False)
