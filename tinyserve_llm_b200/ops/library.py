@@ -25,7 +25,14 @@ def _ptr(t: torch.Tensor | None) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_RAW_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> c_void_p:
+    """The current stream's handle.  Asked for at every launch, so by the short way where torch has one."""
+    if _RAW_STREAM is not None and _RAW_DEVICE is not None:
+        return c_void_p(_RAW_STREAM(_RAW_DEVICE()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
