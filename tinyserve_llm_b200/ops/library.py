@@ -8,7 +8,6 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -21,19 +20,59 @@ class KernelError(RuntimeError):
     """A kernel launcher refused its arguments or the launch failed."""
 
 
-def _ptr(t: torch.Tensor | None) -> c_void_p:
-    return c_void_p(0 if t is None else t.data_ptr())
+# Argument types of the exported functions (p: pointer or stream, i: int, l: long long, f: float), set once
+# on the ctypes functions so that a call converts plain Python numbers itself: at some hundred launches
+# a step, wrapper objects per argument were a tenth of an eager step's host time.
+_SIGNATURES = {
+    "ts_silu_mul": ("int", "ppiiip"),
+    "ts_attention_bf16_scratch_floats": ("long long", "iiii"),
+    "ts_attention_bf16_supported": ("int", "iiii"),
+    "ts_paged_attention_bf16": ("int", "pppplliipippiiiiiiifiplpip"),
+    "ts_paged_attention_generic": ("int", "pppplliipippiiiifiip"),
+    "ts_attention_tcgen05_supported": ("int", "iiiii"),
+    "ts_prefill_attention_tcgen05": ("int", "ppppiiiipippiiiiiifpipp"),
+    "ts_embedding": ("int", "pppiiiip"),
+    "ts_feed_tokens": ("int", "pipip"),
+    "ts_gemm_tcgen05_supported": ("int", "ppiiil"),
+    "ts_gemm_tcgen05": ("int", "pppiiilliipp"),
+    "ts_last_error": ("const char*", ""),
+    "ts_abi_version": ("int", ""),
+    "ts_set_chaining": ("void", "i"),
+    "ts_add_rmsnorm": ("int", "ppppppiifiip"),
+    "ts_copy_page_slots": ("int", "ppiiiiiiiiip"),
+    "ts_rope_store": ("int", "ppppiipipplliiiiiiiip"),
+    "ts_sample_scratch_words": ("int", "ii"),
+    "ts_sample": ("int", "plpppiipip"),
+    "ts_sgemm_nt": ("int", "pppiiilllp"),
+    "ts_skinny_linear_max_rows": ("int", ""),
+    "ts_skinny_linear": ("int", "pppiiilliip"),
+    "ts_skinny_qkv_rope_store": ("int", "pppiilpppiipipplliiiiiip"),
+}
+_CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
+_RETURNS = {"int": ctypes.c_int, "long long": ctypes.c_longlong, "void": None, "const char*": ctypes.c_char_p}
+
+
+def c_int(v):
+    """Arguments go to the library as plain numbers (the functions carry their argument types)."""
+    return v
+
+
+c_longlong = c_float = c_void_p = c_int
+
+
+def _ptr(t: torch.Tensor | None) -> int:
+    return 0 if t is None else t.data_ptr()
 
 
 _RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 _RAW_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
 
 
-def _stream() -> c_void_p:
+def _stream() -> int:
     """The current stream's handle.  Asked for at every launch, so by the short way where torch has one."""
     if _RAW_STREAM is not None and _RAW_DEVICE is not None:
-        return c_void_p(_RAW_STREAM(_RAW_DEVICE()))
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+        return _RAW_STREAM(_RAW_DEVICE())
+    return torch.cuda.current_stream().cuda_stream
 
 
 class Ops:
@@ -45,8 +84,13 @@ class Ops:
             self.lib = ctypes.CDLL(self.lib_path)
         except OSError as exc:
             raise KernelError(f"cannot load the CUDA kernel library {self.lib_path}: {exc}") from None
-        self.lib.ts_last_error.restype = ctypes.c_char_p
-        self.lib.ts_abi_version.restype = c_int
+        for name, (returns, arguments) in _SIGNATURES.items():
+            try:
+                fn = getattr(self.lib, name)
+            except AttributeError:
+                raise KernelError(f"the CUDA kernel library {self.lib_path} does not export {name}") from None
+            fn.restype = _RETURNS[returns]
+            fn.argtypes = [_CTYPES[a] for a in arguments]
         self.launches = 0            # kernels of this library launched (or captured into a graph) so far
         self._error_word: torch.Tensor | None = None
         self.skinny_max_rows = int(self.lib.ts_skinny_linear_max_rows())
@@ -65,9 +109,7 @@ class Ops:
 
     # ------------------------------------------------------------------ helpers
     def _call(self, name: str, *args) -> None:
-        fn = getattr(self.lib, name)
-        fn.restype = c_int
-        if fn(*args) != 0:
+        if getattr(self.lib, name)(*args) != 0:
             raise KernelError(self.lib.ts_last_error().decode())
         self.launches += 1
 
@@ -208,7 +250,6 @@ class Ops:
                     return out
                 max_q_len = 1
             if ctx.min_q_len <= 1:
-                self.lib.ts_attention_bf16_scratch_floats.restype = c_longlong
                 floats = self.lib.ts_attention_bf16_scratch_floats(c_int(num_seqs), c_int(nh), c_int(hd),
                                                                    c_int(ctx.max_ctx_len))
                 key = ("attention", floats)
