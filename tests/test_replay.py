@@ -132,6 +132,34 @@ def test_long_decoding_token_by_token(dtype, model_folders, tmp_path):
     ru.compare(trace, got, want, **(FP32_TOL if dtype == "float32" else bf16_tol(want)))
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_context_of_three_thousand_tokens(dtype, tmp_path):
+    """
+    A longer context than the other tests reach: 3,000 tokens in portions of up to 2,048, then 24 tokens decoded
+    one by one beside a second, short request; a dozen decode splits, 47 pages, rotary scaling past its original
+    window.  Logits of the last portion's end and of every decoded token against the plain implementation.
+    """
+    from tiny_configs import SEED_D, WEIGHTS
+    from tinyserve_llm_b200.weights import write_random_model
+    raw = dict(TINY_D, max_position_embeddings=4096)
+    folder = str(tmp_path / "model")
+    write_random_model(folder, raw, SEED_D, **WEIGHTS)
+    ids = ru.random_ids(raw["vocab_size"], 3024, 61)
+    other = ru.random_ids(raw["vocab_size"], 40, 62)
+    trace = ru.Trace()
+    trace.step([("long", ids[:2048], [2047])])
+    trace.step([("long", ids[2048:2990], [0, 941])])
+    trace.step([("long", ids[2990:3000], [9]), ("other", other[:30], [29])])
+    for i in range(24):
+        parts = [("long", ids[3000 + i:3001 + i], [0])]
+        if i < 10:
+            parts.append(("other", other[30 + i:31 + i], [0]))
+        trace.step(parts, end=(["other"] if i == 9 else []) + (["long"] if i == 23 else []))
+    got = ru.run_trace(folder, dtype, trace, str(tmp_path / "out"))
+    want = ru.plain_logits(folder, {"long": ids, "other": other}, dtype)
+    ru.compare(trace, got, want, **(FP32_TOL if dtype == "float32" else bf16_tol(want)))
+
+
 def test_trace_run_is_a_program_with_the_documented_interface(model_folders, tmp_path):
     """Empty `want`, a request left out of a step, an `end` without entries, and exit code 0 at end of input."""
     ids = ru.random_ids(TINY_A["vocab_size"], 40, 41)
