@@ -298,7 +298,7 @@ def test_kernels_refuse_sizes_they_do_not_take(ops):
         ops.silu_mul(torch.zeros((2, 16), device=DEV)[:, ::2])
 
 
-@pytest.mark.parametrize("vocab", [11, 1000, 128256])
+@pytest.mark.parametrize("vocab", [11, 1000, 8196, 9001, 128256])       # one chunk and several; 16-byte loads and single ones
 def test_sampling_greedy_and_ties(ops, vocab):
     logits = rand((4, vocab), torch.float32, 12)
     logits[1, 5] = logits[1, vocab - 2] = 50.0                     # a tie: the lowest index wins
@@ -327,6 +327,12 @@ def test_sampling_follows_the_softmax_and_its_keys(ops):
     assert torch.equal(again.cpu(), tokens.cpu()[shuffled]), "a draw depends on its key only, not on its row"
     other = ops.sample(logits, temps, torch.tensor([draw_key(2, 0, 0, i) for i in range(draws)], dtype=torch.int32, device=DEV))
     assert (other != tokens).float().mean() > 0.5
+    # the noise of a logit depends on its index and the key only: the same row at the head of a vocabulary of several
+    # chunks, the rest far below, draws the same tokens (another load path, other CTAs, the second kernel's pick)
+    for wide_vocab in (10000, 9001):
+        wide = torch.full((draws, wide_vocab), -1e30)
+        wide[:, :vocab] = row
+        assert torch.equal(ops.sample(wide.to(DEV), temps, keys), tokens)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

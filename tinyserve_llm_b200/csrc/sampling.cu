@@ -55,7 +55,9 @@ __device__ __forceinline__ Best block_best(Best b, float* best_v, int* best_i) {
 
 __device__ __forceinline__ float noisy(float v, int i, float temp, uint32_t k0, uint32_t k1) {
     const uint32_t bits = philox_first_word((uint32_t)i, 0u, k0, k1);
-    const float u = ((float)(bits >> 8) + 0.5f) * (1.0f / 16777216.0f);   // in (0, 1)
+    // 23 bits, so that u + 0.5 ulp is still a float32 below 1: with 24 bits the largest value rounded to 1.0,
+    // whose noise is +infinity, and one logit in 2^24 was drawn whatever its value
+    const float u = ((float)(bits >> 9) + 0.5f) * (1.0f / 8388608.0f);    // in (0, 1), both ends excluded
     const float e = -logf(u);                                              // Exp(1), > 0
     return v / temp - logf(e);
 }
