@@ -335,6 +335,18 @@ def test_sampling_follows_the_softmax_and_its_keys(ops):
         assert torch.equal(ops.sample(wide.to(DEV), temps, keys), tokens)
 
 
+def test_sampling_never_draws_what_has_no_probability(ops):
+    """One logit carries all the probability (the rest: 1e-14 together): every draw over a large vocabulary is that token."""
+    from tinyserve_llm_b200.sampling.sampler import draw_keys
+    vocab, draws = 50000, 4000
+    row = torch.zeros(vocab)
+    row[123] = 30.0
+    logits = row.expand(draws, vocab).contiguous().to(DEV)
+    temps = torch.full((draws,), 0.7, device=DEV)
+    keys = torch.from_numpy(draw_keys(3, [(r, 0, 0) for r in range(draws)])).to(DEV)
+    assert ops.sample(logits, temps, keys).eq(123).all()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_copy_page_slots(ops, dtype):
     shape = (6, 3, 2, 8, 16)
