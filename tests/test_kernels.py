@@ -280,6 +280,45 @@ def test_tensor_core_attention_on_long_batches(ops, hd, g):
         torch.testing.assert_close(got.view(T, -1), same, **tol(torch.bfloat16, 2))
 
 
+@pytest.mark.parametrize("hd, g, page", [(64, 4, 256), (128, 2, 64)])
+def test_decode_attention_over_many_splits(ops, hd, g, page):
+    """Contexts of 17, 20 and 36 decode splits (the combination kernel takes 16 at a time), beside a first token."""
+    nkv = 2
+    nh = nkv * g
+    ctx_lens = [4097, 9000, 5000, 1]
+    q_lens = [1, 1, 1, 1]
+    ctx = make_ctx(q_lens, ctx_lens)
+    tables, at = [], 0
+    for c in ctx_lens:
+        n = -(-c // page)
+        tables.append(list(range(at, at + n)))
+        at += n
+    binding = make_binding(at + 1, 1, nkv, page, hd, torch.bfloat16, tables)
+    keys = [rand((c, nkv, hd), torch.bfloat16, 60 + s) for s, c in enumerate(ctx_lens)]
+    values = [rand((c, nkv, hd), torch.bfloat16, 70 + s) for s, c in enumerate(ctx_lens)]
+    for s in range(len(ctx_lens)):
+        table = binding.block_table[s].tolist()                        # whole pages at once: a slot at a time is slow here
+        for i in range(-(-ctx_lens[s] // page)):
+            n = min(page, ctx_lens[s] - i * page)
+            binding.k_pool[table[i], 0, :, :n] = keys[s][i * page:i * page + n].transpose(0, 1).to(DEV)
+            binding.v_pool[table[i], 0, :, :n] = values[s][i * page:i * page + n].transpose(0, 1).to(DEV)
+    qkv = rand((4, (nh + 2 * nkv) * hd), torch.bfloat16, 13)
+    qkv[1, :hd] = (keys[1][4100, 0].float() * 3).to(torch.bfloat16)      # request 1, head 0 attends to a key in its seventeenth split
+    scale = hd ** -0.5
+    got = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0).cpu().double().view(4, nh, hd)
+    want = torch.zeros_like(got)
+    for s in range(4):
+        q = qkv[s, : nh * hd].view(nh, hd).double()
+        for h in range(nh):
+            k, v = keys[s][:, h // g].double(), values[s][:, h // g].double()
+            p = torch.softmax(k @ q[h] * scale, dim=0)
+            want[s, h] = plain.rnd(p, "bfloat16") @ v
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, plain.rnd(want, "bfloat16"), **tol(torch.bfloat16, 2))
+    same = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0, generic=True).cpu().double()
+    torch.testing.assert_close(got.view(4, -1), same, **tol(torch.bfloat16, 2))
+
+
 def test_kernels_refuse_sizes_they_do_not_take(ops):
     from tinyserve_llm_b200.ops.library import KernelError
     ctx = make_ctx([1], [1])
