@@ -73,9 +73,19 @@ def peaks() -> tuple[dict, str]:
             with open(path) as f:
                 data = json.load(f)
             flat = {}
-            for k, v in data.items():
-                if isinstance(v, (int, float)):
-                    flat[k] = float(v)
+
+            def walk(node) -> None:               # the keys may sit at the top or inside a nested record
+                if isinstance(node, dict):
+                    for k, v in node.items():
+                        if isinstance(v, (int, float)) and not isinstance(v, bool):
+                            flat.setdefault(k, float(v))
+                        else:
+                            walk(v)
+                elif isinstance(node, list):
+                    for v in node:
+                        walk(v)
+
+            walk(data)
             if "hbm_gbs" in flat and "bf16_tflops" in flat:
                 return flat, "measured"
         except (OSError, ValueError):
