@@ -14,6 +14,7 @@ L2).  `e2e` is the same through LLM.step(): host token ids in, host token ids ou
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -176,7 +177,6 @@ def run_ours(args) -> dict:
                                       prefill_chunk=2048, watermark=0.0),
               CacheConfig(block_size=PAGE, caching=False), dtype="bfloat16", num_blocks=pages, seed=0,
               random_weights_seed=0)
-    llm.run_ahead = False          # the device-timed parts below drive the step function themselves, between whole steps
     ops, runner, cache = llm.model.rt.ops, llm.runner, llm.cache
     gen = torch.Generator().manual_seed(0)
 
@@ -197,35 +197,51 @@ def run_ours(args) -> dict:
         while llm.scheduler.has_unfinished():
             llm.step()
 
+    @contextlib.contextmanager
+    def held_contexts(batch: int, context: int):
+        """
+        `batch` requests of `context` tokens in the cache, each with the slot of its next token reserved: the
+        entries of one decode step, which the timed loops run again and again (every run rewrites the same slots).
+        The step function and the cache manager are driven directly; the scheduler holds none of these requests.
+        """
+        ids = [("held", batch, context, i) for i in range(batch)]
+        for seq_id, tokens in zip(ids, prompts(batch, context)):
+            for at in range(0, context, PREFILL_TOKENS):      # the step function takes what was reserved, whole
+                part = tokens[at:at + PREFILL_TOKENS]
+                if at == 0:
+                    assert cache.admit(seq_id, part), "the cache pool is too small for the measurement"
+                else:
+                    cache.extend(seq_id, part)
+                runner.step([StepEntry(seq_id, part, [])])
+                cache.commit(seq_id, len(part))
+        entries = []
+        for n, seq_id in enumerate(ids):
+            cache.extend(seq_id, [n + 1])
+            entries.append(StepEntry(seq_id, [n + 1], [0]))
+        try:
+            yield entries
+        finally:
+            torch.cuda.synchronize()
+            for seq_id in ids:
+                cache.commit(seq_id, 1)
+                cache.release(seq_id)
+
     def device_decode(batch: int, context: int, k: int, w: int):
         """K decode steps timed on the device: graph replay + sampling kernel, no host read in between."""
-        start_decoding(batch, context, w + k + 2 + 512)      # room for the tokens decoded while the others still prefill
-        seqs = list(llm.scheduler.running)
-        assert len(seqs) == batch, f"{len(seqs)} of {batch} requests are decoding"
-        entries = []
-        for s in seqs:                                    # reserve the step's slot as the scheduler would
-            cache.extend(s.seq_id, [s.output_token_ids[-1]])
-            entries.append(StepEntry(s.seq_id, [s.output_token_ids[-1]], [0]))
         temps = torch.zeros(batch, dtype=torch.float32, device=llm.device)
         keys = torch.zeros((batch, 2), dtype=torch.int32, device=llm.device)
-        for _ in range(w):
-            ops.sample(runner.step(entries), temps, keys)
-        torch.cuda.synchronize()
-        before = ops.launches
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        begin.record()
-        for _ in range(k):
-            ops.sample(runner.step(entries), temps, keys)
-        end.record()
-        torch.cuda.synchronize()
-        ms = begin.elapsed_time(end) / k
-        launches = ops.launches - before
-        for s in seqs:
-            cache.commit(s.seq_id, 1)
-        for s in seqs:                                    # hand the sequences back in a consistent state
-            s.output_token_ids.append(0)
-        finish_all()
-        return ms, launches
+        with held_contexts(batch, context) as entries:
+            for _ in range(w):
+                ops.sample(runner.step(entries), temps, keys)
+            torch.cuda.synchronize()
+            before = ops.launches
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            for _ in range(k):
+                ops.sample(runner.step(entries), temps, keys)
+            end.record()
+            torch.cuda.synchronize()
+            return begin.elapsed_time(end) / k, ops.launches - before
 
     # ---- prefill of 2,048 tokens, whole, device timed
     def prefill_once(seq_id: int) -> float:
@@ -249,20 +265,16 @@ def run_ours(args) -> dict:
             prefill_once(99)
             torch.cuda.profiler.stop()
         else:
-            start_decoding(BATCH, CONTEXT, 64 + 512)
-            entries = []
-            for s in list(llm.scheduler.running):
-                cache.extend(s.seq_id, [s.output_token_ids[-1]])
-                entries.append(StepEntry(s.seq_id, [s.output_token_ids[-1]], [0]))
             temps = torch.zeros(BATCH, dtype=torch.float32, device=llm.device)
             keys = torch.zeros((BATCH, 2), dtype=torch.int32, device=llm.device)
-            for _ in range(3):
+            with held_contexts(BATCH, CONTEXT) as entries:
+                for _ in range(3):
+                    ops.sample(runner.step(entries), temps, keys)
+                torch.cuda.synchronize()
+                torch.cuda.profiler.start()
                 ops.sample(runner.step(entries), temps, keys)
-            torch.cuda.synchronize()
-            torch.cuda.profiler.start()
-            ops.sample(runner.step(entries), temps, keys)
-            torch.cuda.synchronize()
-            torch.cuda.profiler.stop()
+                torch.cuda.synchronize()
+                torch.cuda.profiler.stop()
         return {"impl": "ours", "profiled": f"one {args.profile_step} step", "config": {"model": model_name, "layers": layers}}
     prefill_ms = statistics.median(prefill_once(10 + i) for i in range(5))
 
@@ -270,7 +282,6 @@ def run_ours(args) -> dict:
     with ClockSampler() as clocks:
         ms, launches = device_decode(BATCH, CONTEXT, steps, warmup)
         # ---- end to end through the entry point: host token ids in, host token ids out
-        llm.run_ahead = True       # the entry point's default
         start_decoding(BATCH, CONTEXT, warmup + steps + 2 + 512)
         for _ in range(warmup):
             llm.step()
@@ -281,7 +292,6 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
         e2e_seconds = time.perf_counter() - t0
         finish_all()
-        llm.run_ahead = False
     graph = runner._graphs.get(runner.bucket(BATCH))
     h2d = (graph.index_buffer.numel() * 4 if graph else 0) + BATCH * 3 * 4
     points = {}
@@ -289,30 +299,22 @@ def run_ours(args) -> dict:
         pms, _ = device_decode(b, point_context, max(10, steps // 2), 3)
         points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
     # a mixed step: 64 requests decoding beside one 2,048-token prompt portion
-    start_decoding(64, point_context, 8 + 512)
-    mixed_entries = []
-    for sq in llm.scheduler.running:
-        cache.extend(sq.seq_id, [sq.output_token_ids[-1]])
-        mixed_entries.append(StepEntry(sq.seq_id, [sq.output_token_ids[-1]], [0]))
     chunk = prompts(1, PREFILL_TOKENS)[0]
-    assert cache.admit(("mixed", 0), chunk)
-    mixed_entries.append(StepEntry(("mixed", 0), chunk, [PREFILL_TOKENS - 1]))
-    for _ in range(2):
-        runner.step(mixed_entries)
-    torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
-    for _ in range(5):
-        runner.step(mixed_entries)
-    end.record()
-    torch.cuda.synchronize()
-    mixed_ms = begin.elapsed_time(end) / 5
-    cache.commit(("mixed", 0), PREFILL_TOKENS)
-    cache.release(("mixed", 0))
-    for sq in list(llm.scheduler.running):
-        cache.commit(sq.seq_id, 1)
-        sq.output_token_ids.append(0)
-    finish_all()
+    with held_contexts(64, point_context) as decodes:
+        assert cache.admit(("mixed", 0), chunk)
+        mixed_entries = decodes + [StepEntry(("mixed", 0), chunk, [PREFILL_TOKENS - 1])]
+        for _ in range(2):
+            runner.step(mixed_entries)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(5):
+            runner.step(mixed_entries)
+        end.record()
+        torch.cuda.synchronize()
+        mixed_ms = begin.elapsed_time(end) / 5
+        cache.commit(("mixed", 0), PREFILL_TOKENS)
+        cache.release(("mixed", 0))
 
     value = BATCH / ms * 1e3
     moved = weight_bytes(cfg, layers) + kv_bytes(cfg, layers, BATCH, CONTEXT)
