@@ -495,6 +495,41 @@ def test_tcgen05_prompt_attention(ops, nh, nkv, page, hd):
     torch.testing.assert_close(got, legacy, **tol(torch.bfloat16, 2))
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_tcgen05_prompt_attention_when_the_maximum_grows_from_tile_to_tile(ops, hd):
+    """
+    The kernel rescales O only when a row's maximum has grown by more than 2^8 since its reference was
+    taken.  Keys are scaled so that the scores of one query direction grow along the sequence: by small steps
+    (the reference stays, P holds values above one), then by a jump of hundreds (the reference moves and what
+    was summed before all but vanishes), then fall again.  Random inputs alone never leave the first case.
+    """
+    nh, nkv, page, T = 4, 2, 128, 1500
+    ctx = make_ctx([T], [T])
+    binding = make_binding(-(-T // page) + 1, 1, nkv, page, hd, torch.bfloat16, [list(range(-(-T // page)))], entry=0)
+    direction = torch.nn.functional.normalize(rand((hd,), torch.float32, 70), dim=0)
+    keys = rand((T, nkv, hd), torch.bfloat16, 71).float() * 0.3
+    at = torch.arange(T, dtype=torch.float32)
+    # the score against `direction` (log2 units after the scale): +1.5 a tile of 128 keys up to key 900, +400 from
+    # key 900 to 1100, back to nothing after it
+    ramp = torch.where(at < 900, at / 128 * 1.5, torch.where(at < 1100, torch.full_like(at, 400.0), torch.zeros_like(at)))
+    scale = hd ** -0.5
+    keys[:, 0, :] += (ramp / (scale * math.log2(math.e)))[:, None] * direction[None, :] / 8.0
+    keys = keys.to(torch.bfloat16)
+    values = rand((T, nkv, hd), torch.bfloat16, 72)
+    fill_cache(binding, 0, keys, values, entry=0)
+    qkv = rand((T, (nh + 2 * nkv) * hd), torch.bfloat16, 73) * 0.3
+    qkv[:, :hd] += (direction * 8.0).to(torch.bfloat16)                 # head 0 (kv head 0) looks along the direction
+    got = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0).cpu().double().view(T, nh, hd)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    want = plain_paged_attention(qkv[:, : nh * hd].view(T, nh, hd).double(), [keys], [values], [T], [T], scale, 0)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, plain.rnd(want, "bfloat16"), **tol(torch.bfloat16, 2))
+    # the case is what it says: along head 0 the largest score of a row grows by more than 2^8 in one step
+    s0 = (qkv[1099, :hd].double() @ keys[:1100, 0].double().T) * scale * math.log2(math.e)
+    assert s0[900:].max() - s0[:900].max() > 100 and 2 < s0[:900].max() - s0[:128].max() < 40
+
+
 def test_environment_switches(ops, monkeypatch):
     """The library's switches are read when it is loaded; serialised launches give the same bits as chained ones."""
     from tinyserve_llm_b200.ops.library import Ops

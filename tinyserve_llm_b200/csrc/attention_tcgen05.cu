@@ -6,17 +6,20 @@
 //   * S = Q K^T for a tile of 128 keys is one tcgen05.mma chain (A = the query tile, B = the key
 //     tile, both brought into 128-byte-swizzled shared memory by TMA straight from the qkv matrix
 //     and from the paged pool) into tensor memory;
-//   * thread r of the four softmax warps owns query row r, which is lane r of tensor memory: it reads
-//     its row of S with tcgen05.ld, keeps the running maximum and sum in float32 with no exchange
-//     between threads, writes P = exp2(S - m) as bfloat16 pairs back into tensor memory over S
-//     (tcgen05.st) and rescales its row of O;
+//   * two threads of the eight softmax warps own query row r, which is lane r of tensor memory: each reads
+//     its half of the row of S with tcgen05.ld into registers, they exchange their maxima, keep the
+//     reference of the exponentials and the sum in float32, write P = exp2(S - m) as bfloat16 pairs into
+//     tensor-memory columns of P's own (tcgen05.st) and rescale their halves of the row of O, which is
+//     needed only when the maximum has grown by more than 2^8 since the reference was taken;
 //   * O += P V is a second tcgen05.mma chain with A = P read from tensor memory and B = the value
 //     tile as it lies in shared memory (dims contiguous: the MN-major operand form).
 //
-// Warp 4 is the TMA producer over a two-stage ring of key/value tiles, warp 5 allocates tensor memory
-// and issues the MMAs, warps 0..3 are the softmax.  Hand-offs are mbarriers: kv_full (TMA bytes),
-// s_done / stage_free / all_done (tcgen05.commit) and p_ready (128 thread arrivals).  Two CTAs share
-// an SM, so one's softmax runs under the other's MMAs.  A query at position p sees keys 0..p
+// Warp 8 is the TMA producer over a two-stage ring of key/value tiles, warp 9 allocates tensor memory
+// and issues the MMAs, warps 0..7 are the softmax.  Hand-offs are mbarriers: kv_full (TMA bytes),
+// s_done / stage_free / all_done (tcgen05.commit) and p_ready (256 thread arrivals).  When the softmax
+// hands over P of a tile, the scores of the next tile are issued before this tile's O += P V, so that
+// the next softmax begins under that product.  Two CTAs share an SM, so one's softmax runs under the
+// other's MMAs.  A query at position p sees keys 0..p
 // (attention/torch_paged.py:36-45 of the reference, by positions); value rows beyond the request's
 // length are zeroed in shared memory before they are multiplied.
 //
@@ -49,6 +52,7 @@ constexpr int SOFTMAX_WARPS = 8;             // two threads a query row: each ta
 constexpr int PRODUCER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1, THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr long long WAIT_CYCLES = 4000000000ll;
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_STEP = 8.f;          // in powers of two
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
@@ -180,7 +184,7 @@ struct FlashParams {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(THREADS) prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         FlashParams p) {
@@ -272,20 +276,30 @@ __global__ void __launch_bounds__(THREADS) prefill_attention_tcgen05_kernel(cons
         const uint32_t idesc_s = instr_desc(QROWS, KEYS, false);
         const uint32_t idesc_o = instr_desc(QROWS, 64, true);        // O in column blocks of 64 dims, one per sub-tile of V
         bool ok = mbar_wait(&q_full, 0, p.error, 12);
-        for (int j = 0; j < num_kv && ok; ++j) {
+        // S = Q K^T of tile j, once its keys have landed
+        auto issue_scores = [&](int j) -> bool {
             const int s = j & 1;
-            if (!mbar_wait(&kv_full[s], (j >> 1) & 1, p.error, 13)) { ok = false; break; }
+            if (!mbar_wait(&kv_full[s], (j >> 1) & 1, p.error, 13)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int h = 0; h < SUBS; ++h) {         // S = Q K^T; the tensor pipe runs the chains in order, after O += P V of the tile before
+            for (int h = 0; h < SUBS; ++h) {
                 const uint64_t q_desc = smem_desc(q_tile + h * SUB_Q);
                 const uint64_t k_desc = smem_desc(kv_tiles + s * STAGE_BYTES + h * SUB_KV);
 #pragma unroll
                 for (int k = 0; k < 4; ++k) umma_ss(tmem, q_desc + 2 * k, k_desc + 2 * k, idesc_s, (h | k) != 0);
             }
             umma_commit(&s_done);
+            return true;
+        };
+        ok = ok && issue_scores(0);
+        for (int j = 0; j < num_kv && ok; ++j) {
+            const int s = j & 1;
             if (!mbar_wait(&p_ready, j & 1, p.error, 14)) { ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // The softmax has read S of tile j (P lies in columns of its own), so the next tile's scores go first:
+            // its softmax can begin while O += P V of this tile is still running.  The softmax waits for that
+            // product (stage_free) before it writes P again or rescales O.
+            if (j + 1 < num_kv && !issue_scores(j + 1)) { ok = false; break; }
 #pragma unroll
             for (int h = 0; h < SUBS; ++h) {         // O += P V: 16 keys are 8 columns of packed P and 16 rows (2048 bytes) of a V sub-tile
                 const uint64_t v_desc = smem_desc(kv_tiles + s * STAGE_BYTES + KV_BYTES + h * SUB_KV);
@@ -324,38 +338,54 @@ __global__ void __launch_bounds__(THREADS) prefill_attention_tcgen05_kernel(cons
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const bool masked = key0 + KEYS - 1 > pos0;        // some row of the tile does not see all of these keys
-            // pass 1: the maximum over this thread's keys (four running maxima: no long dependent chain).  Reading S
-            // twice from tensor memory measured faster than holding the row in registers.
+            // this thread's keys of S come into registers once, all loads under way together
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll 1
-            for (int c = col0; c < col0 + HK; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(lane_addr + c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            uint32_t sv[HK / 32][32];
+#pragma unroll
+            for (int ch = 0; ch < HK / 32; ++ch) tmem_ld32(lane_addr + col0 + ch * 32, sv[ch]);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // pass 1: the maximum over them (four running maxima: no long dependent chain)
+#pragma unroll
+            for (int ch = 0; ch < HK / 32; ++ch) {
+                const int c = col0 + ch * 32;
                 if (masked) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        if (key0 + c + i <= pos) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
+                        if (key0 + c + i <= pos) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[ch][i]));
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(v[i]));
+                    for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[ch][i]));
                 }
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             half_max[j & 1][half][r] = mx;
             pair_barrier(quadrant);
             mx = fmaxf(mx, half_max[j & 1][half ^ 1][r]);
-            const float m_new = fmaxf(m_run, mx * p.scale_log2);
+            // O += P V of the tile before must have retired before P is written again and O is rescaled
+            if (j > 0 && !mbar_wait(&stage_free[(j - 1) & 1], ((j - 1) >> 1) & 1, p.error, 17)) ok = false;
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                mbar_arrive(&p_ready);
+                continue;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // The reference the exponentials are taken against follows the maximum only when that has grown by
+            // more than RESCALE_STEP: until then P holds values up to 2^RESCALE_STEP, which float32 sums and
+            // bfloat16 products take without loss, and O needs no rescaling (softmax does not depend on the
+            // reference it is computed against).
+            const float m_tile = mx * p.scale_log2;
+            const bool moved = m_tile > m_run + RESCALE_STEP;          // also the first tile that shows the row a key
+            const float m_new = moved ? m_tile : m_run;
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = fast_exp2(m_run - m_use);
+            const float corr = moved ? fast_exp2(m_run - m_use) : 1.f;
             m_run = m_new;
             // pass 2: P = exp2(S * scale - m) as bfloat16 pairs into P's own columns (pair i covers keys 2i, 2i+1)
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-            for (int c = col0; c < col0 + HK; c += 32) {
-                uint32_t v[32], packed[16];
-                tmem_ld32(lane_addr + c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int ch = 0; ch < HK / 32; ++ch) {
+                const int c = col0 + ch * 32;
+                uint32_t packed[16];
+                const uint32_t (&v)[32] = sv[ch];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
