@@ -51,6 +51,7 @@ struct Shape {
 constexpr int SOFTMAX_WARPS = 8;             // two threads a query row: each takes half of the tile's keys and half of O's dims
 constexpr int PRODUCER_WARP = SOFTMAX_WARPS, MMA_WARP = SOFTMAX_WARPS + 1, THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr long long WAIT_CYCLES = 4000000000ll;
+constexpr uint32_t SUSPEND_NS = 1000000;      // a waiting thread may sleep this long in one try before it looks at the clock
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.f;          // in powers of two
 
@@ -70,9 +71,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* e
     while (true) {
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+            : "=r"(done) : "r"(smem_u32(bar)), "r"(parity), "r"(SUSPEND_NS) : "memory");
         if (done) return true;
         if (clock64() - start > WAIT_CYCLES) {
             atomicExch(error, code);
@@ -379,29 +380,45 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float corr = moved ? fast_exp2(m_run - m_use) : 1.f;
             m_run = m_new;
-            // pass 2: P = exp2(S * scale - m) as bfloat16 pairs into P's own columns (pair i covers keys 2i, 2i+1)
+            // pass 2: P = exp2(S * scale - m) as bfloat16 pairs into P's own columns (pair i covers keys 2i, 2i+1).
+            // The tile on the diagonal has a loop of its own: inside one loop the compiler keeps the compare
+            // and select of every element in the instruction stream of the tiles that need none.
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
+            if (masked) {
 #pragma unroll
-            for (int ch = 0; ch < HK / 32; ++ch) {
-                const int c = col0 + ch * 32;
-                uint32_t packed[16];
-                const uint32_t (&v)[32] = sv[ch];
+                for (int ch = 0; ch < HK / 32; ++ch) {
+                    const int c = col0 + ch * 32;
+                    uint32_t packed[16];
+                    const uint32_t (&v)[32] = sv[ch];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
-                    float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
-                    if (masked) {
+                    for (int i = 0; i < 32; i += 2) {
+                        float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+                        float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
                         if (key0 + c + i > pos) p0 = 0.f;
                         if (key0 + c + i + 1 > pos) p1 = 0.f;
+                        l4[(i >> 1) & 3] += p0 + p1;
+                        packed[i >> 1] = pack_bf16(p0, p1);
                     }
-                    l4[(i >> 1) & 3] += p0 + p1;
-                    packed[i >> 1] = pack_bf16(p0, p1);
+                    tmem_st16(lane_addr + P_COL + (c >> 1), packed);
                 }
-                tmem_st16(lane_addr + P_COL + (c >> 1), packed);
+            } else {
+#pragma unroll
+                for (int ch = 0; ch < HK / 32; ++ch) {
+                    const int c = col0 + ch * 32;
+                    uint32_t packed[16];
+                    const uint32_t (&v)[32] = sv[ch];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_use));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_use));
+                        l4[(i >> 1) & 3] += p0 + p1;
+                        packed[i >> 1] = pack_bf16(p0, p1);
+                    }
+                    tmem_st16(lane_addr + P_COL + (c >> 1), packed);
+                }
             }
             l_run = l_run * corr + ((l4[0] + l4[1]) + (l4[2] + l4[3]));
-            // this thread's dims of O follow the new maximum (O's last update has retired: S of this tile came
-            // after it); skipped when no row of the warp moved its maximum
+            // this thread's dims of O follow the new reference; skipped when no row of the warp moved it
             if (j > 0 && !__all_sync(0xffffffffu, corr == 1.f)) {
 #pragma unroll 1
                 for (int c = half * HO; c < half * HO + HO; c += 32) {
