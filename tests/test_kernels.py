@@ -317,6 +317,26 @@ def test_decode_attention_over_many_splits(ops, hd, g, page):
     torch.testing.assert_close(got, plain.rnd(want, "bfloat16"), **tol(torch.bfloat16, 2))
     same = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0, generic=True).cpu().double()
     torch.testing.assert_close(got.view(4, -1), same, **tol(torch.bfloat16, 2))
+    # How a request's splits are merged depends on its own length only: alone or beside the 9,000-token request
+    # (where the combination runs with more threads a block) it gives the same bits.  4,097 tokens are 17 splits.
+    for s, c in ((0, 4097), (2, 5000), (3, 1)):
+        alone_ctx = make_ctx([1], [c])
+        alone = make_binding(at + 1, 1, nkv, page, hd, torch.bfloat16, [tables[s]])
+        alone.k_pool.copy_(binding.k_pool)
+        alone.v_pool.copy_(binding.v_pool)
+        one = ops.paged_attention(qkv[s:s + 1].to(DEV), alone_ctx, alone, nh, nkv, hd, scale, 0).cpu().double()
+        assert torch.equal(one.view(nh, hd), got[s]), f"request {s} depends on its neighbours"
+    short_ctx = make_ctx([1, 1], [5000 - 4000, 1])        # up to 16 splits everywhere: the combination with one group
+    few = make_binding(at + 1, 1, nkv, page, hd, torch.bfloat16, [tables[2], tables[3]])
+    few.k_pool.copy_(binding.k_pool)
+    few.v_pool.copy_(binding.v_pool)
+    long_ctx = make_ctx([1, 1], [5000 - 4000, 9000])
+    many = make_binding(at + 1, 1, nkv, page, hd, torch.bfloat16, [tables[2], tables[1]])
+    many.k_pool.copy_(binding.k_pool)
+    many.v_pool.copy_(binding.v_pool)
+    a = ops.paged_attention(qkv[2:4].to(DEV), short_ctx, few, nh, nkv, hd, scale, 0)[0]
+    b = ops.paged_attention(qkv[2:4].to(DEV), long_ctx, many, nh, nkv, hd, scale, 0)[0]
+    assert torch.equal(a, b), "a short request is merged the same way whatever the step's longest request is"
 
 
 def test_kernels_refuse_sizes_they_do_not_take(ops):

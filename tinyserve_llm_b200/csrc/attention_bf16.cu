@@ -470,11 +470,18 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
     }
 }
 
-// One block per (request, head): merges the splits in order and writes the output row.  The loads
-// of a chunk of splits are all issued before any is used, so that the kernel pays a memory latency
-// or two, not one per split.
-template <int HD>
-__global__ void decode_combine_kernel(AttnParams p) {
+// One block per (request, head): merges the splits and writes the output row.  The block is GROUPS groups
+// of HD threads (one per dim); a group takes a contiguous share of the splits, loads a chunk of them at
+// once (so that it pays a memory latency or two, not one per split) and merges them in order against its
+// own maximum; the groups' results are merged in group order.  A request of up to one chunk of splits is
+// merged by the first group alone, and longer ones are always shared among 256 / HD groups (the launch
+// has them whenever the step's longest request needs them): how a request's splits are merged depends on
+// its own length only, never on what else is in the step.
+constexpr int COMBINE_CHUNK = 16;
+template <int HD, int GROUPS>
+__global__ void __launch_bounds__(GROUPS * HD) decode_combine_kernel(AttnParams p) {
+    __shared__ float group_o[GROUPS][HD];
+    __shared__ float2 group_ml[GROUPS];
     const int seq = blockIdx.y, head = blockIdx.x;
     const int q_begin = p.cu_q[seq];              // index data: written by the host before the step
     const int q_len = p.cu_q[seq + 1] - q_begin;
@@ -485,26 +492,28 @@ __global__ void decode_combine_kernel(AttnParams p) {
     const int splits = (ctx + SPLIT - 1) / SPLIT;
     const float* part_o = p.partial_o + ((long long)seq * p.nh + head) * p.max_splits * HD;
     const float2* part_ml = reinterpret_cast<const float2*>(p.partial_ml) + ((long long)seq * p.nh + head) * p.max_splits;
-    const int d = threadIdx.x;
-    constexpr int CH = 16;
+    const int group = threadIdx.x / HD, d = threadIdx.x % HD;
+    const int share = splits <= COMBINE_CHUNK ? splits : (splits + GROUPS - 1) / GROUPS;
+    const int s_begin = min(group * share, splits), s_end = min(s_begin + share, splits);
+    constexpr int CH = COMBINE_CHUNK;
     float2 ml[CH];
     float ov[CH];
 #pragma unroll
     for (int j = 0; j < CH; ++j) {
-        const bool ok = j < splits;
-        ml[j] = ok ? part_ml[j] : make_float2(-INFINITY, 0.f);
-        ov[j] = ok ? part_o[(long long)j * HD + d] : 0.f;
+        const bool ok = s_begin + j < s_end;
+        ml[j] = ok ? part_ml[s_begin + j] : make_float2(-INFINITY, 0.f);
+        ov[j] = ok ? part_o[(long long)(s_begin + j) * HD + d] : 0.f;
     }
     float m = -INFINITY;
 #pragma unroll
     for (int j = 0; j < CH; ++j) m = fmaxf(m, ml[j].x);
-    for (int s = CH; s < splits; ++s) m = fmaxf(m, part_ml[s].x);
+    for (int s = s_begin + CH; s < s_end; ++s) m = fmaxf(m, part_ml[s].x);
     float l = 0.f, o = 0.f;
-    for (int s0 = 0; s0 < splits; s0 += CH) {
-        if (s0 > 0) {
+    for (int s0 = s_begin; s0 < s_end; s0 += CH) {
+        if (s0 > s_begin) {
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-                const bool ok = s0 + j < splits;
+                const bool ok = s0 + j < s_end;
                 ml[j] = ok ? part_ml[s0 + j] : make_float2(-INFINITY, 0.f);
                 ov[j] = ok ? part_o[(long long)(s0 + j) * HD + d] : 0.f;
             }
@@ -516,6 +525,21 @@ __global__ void decode_combine_kernel(AttnParams p) {
             l += ml[j].y * f;
             o += ov[j] * f;
         }
+    }
+    group_o[group][d] = o;
+    if (d == 0) group_ml[group] = make_float2(m, l);
+    __syncthreads();
+    if (group != 0) return;
+    float top = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) top = fmaxf(top, group_ml[g].x);
+    l = 0.f, o = 0.f;
+#pragma unroll
+    for (int g = 0; g < GROUPS; ++g) {
+        if (group_ml[g].x == -INFINITY) continue;         // a group without a key
+        const float f = fast_exp2(group_ml[g].x - top);
+        l += group_ml[g].y * f;
+        o += group_o[g][d] * f;
     }
     p.out[((long long)q_begin * p.nh + head) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
 }
@@ -540,8 +564,12 @@ int launch(const AttnParams& p, int max_q_len, int min_q_len, int max_ctx_len, i
         if (splits > p.max_splits) return ts_fail("decode_attention: %d splits needed, scratch holds %d", splits, p.max_splits);
         dim3 grid(splits, p.nkv, p.num_seqs);
         TS_CHAINED_CHECK("decode_attention", launch_chained(kernel, grid, dim3(DW * 32), smem, stream, p));
-        TS_CHAINED_CHECK("decode_combine", launch_chained(decode_combine_kernel<HD>, dim3(p.nh, p.num_seqs), dim3(HD), 0,
-                                                          stream, p));
+        if (splits <= COMBINE_CHUNK)
+            TS_CHAINED_CHECK("decode_combine", launch_chained(decode_combine_kernel<HD, 1>, dim3(p.nh, p.num_seqs), dim3(HD), 0,
+                                                              stream, p));
+        else
+            TS_CHAINED_CHECK("decode_combine", launch_chained(decode_combine_kernel<HD, 256 / HD>, dim3(p.nh, p.num_seqs),
+                                                              dim3(256), 0, stream, p));
     }
     return 0;
 }
