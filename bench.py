@@ -291,8 +291,8 @@ def run_ours(args) -> dict:
             llm.step()
         torch.cuda.synchronize()
         e2e_seconds = time.perf_counter() - t0
+        graph = runner.last_graph      # the graph the end-to-end steps replayed
         finish_all()
-    graph = runner._graphs.get(runner.bucket(BATCH))
     h2d = (graph.index_buffer.numel() * 4 if graph else 0) + BATCH * 3 * 4
     points = {}
     for b in (1, 8, 64):

@@ -227,6 +227,48 @@ def test_a_token_fed_on_the_device_gives_the_step_the_host_token_gives(model_fol
     assert torch.equal(results[0], results[2]) and torch.equal(results[1], results[3])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_graphs_follow_the_longest_request(model_folders, dtype):
+    """
+    A decode graph is captured for a bucket of the batch size and of the pages the step's longest request
+    holds, not for the longest context the engine allows.  Decoding across the edges of those buckets
+    (the tables grow from 2 pages to 8 here) gives bit for bit what steps without graphs give, and a short
+    batch after a long one goes back to the small graph.
+    """
+    from tinyserve_llm_b200.engine.loading import build_cache, load_model
+    from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
+    assert [StepRunner.width_bucket(n) for n in (1, 2, 3, 4, 5, 6, 7, 9, 13, 17, 25, 33)] == [1, 2, 3, 4, 6, 6, 8, 12, 16, 24, 32, 48]
+    model = load_model(model_folders["b"], dtype, "cuda")
+    vocab = TINY_B["vocab_size"]
+    prompts = [ru.random_ids(vocab, n, 90 + n) for n in (PAGE_B + 3, 2 * PAGE_B - 2, 5)]
+    steps = 5 * PAGE_B + 4
+    outs = {}
+    for graphs in (True, False):
+        _, manager, storage = build_cache(model, PAGE_B, 40, caching=False)
+        runner = StepRunner(model, manager, storage, cuda_graphs=graphs, max_model_len=30 * PAGE_B)
+        for i, p in enumerate(prompts):
+            assert manager.admit(i, p)
+        runner.step([StepEntry(i, p, []) for i, p in enumerate(prompts)])
+        for i, p in enumerate(prompts):
+            manager.commit(i, len(p))
+        got, expected = [], set()
+        for t in range(steps):
+            live = [0, 1, 2] if t < steps - 3 else [2]            # at the end the short request alone
+            for i in live:
+                manager.extend(i, [(7 * t + i) % vocab])
+            expected.add(StepRunner.width_bucket(max(len(manager.seqs[i].tables[0]) for i in live)))
+            got.append(runner.step([StepEntry(i, [(7 * t + i) % vocab], [0]) for i in live]).cpu().clone())
+            for i in live:
+                manager.commit(i, 1)
+        outs[graphs] = got
+        if graphs:
+            widths = {key[1][0] for key in runner._graphs}
+            assert widths == expected and len(widths) >= 5, (widths, expected)    # 2 pages at first, 8 at the end
+            assert runner.graph_replays == steps
+    for a, b in zip(outs[True], outs[False]):
+        assert torch.equal(a, b)
+
+
 def test_multi_turn_replay_reuses_histories_and_changes_no_token(model_folders, tmp_path):
     """The multi-turn replay runner: with the prefix cache on, later turns prefill only what is new; the replies are the same."""
     from tinyserve_llm_b200.cli import multiturn

@@ -84,7 +84,7 @@ def _pad4(n: int) -> int:
 
 
 class _DecodeGraph:
-    """A captured decode step for one batch size: static index buffer in, static logits out."""
+    """A captured decode step for one batch size and one bound on the requests' pages: static index buffer in, static logits out."""
 
     def __init__(self, graph: torch.cuda.CUDAGraph, index_buffer: torch.Tensor, logits: torch.Tensor,
                  widths: list[int], launches: int) -> None:
@@ -98,9 +98,13 @@ class _DecodeGraph:
 class StepRunner:
     """
     `cuda_graphs`: steps in which every request feeds one token (decoding) are replayed from a CUDA
-    graph captured per batch-size bucket, when every part of the model is graph safe.  The logits
-    such a step returns live in the graph's static buffer and are overwritten by the next decode
-    step of the same bucket: consume them (sample, copy) before stepping again.
+    graph, when every part of the model is graph safe.  A graph is captured per bucket of the batch size
+    and of the pages the step's longest request holds (both powers of two): the attention's grid
+    covers what the block tables can hold, so a graph sized for the longest context the engine allows
+    would make every step pay for it (64 requests of 512 tokens: 1.26 ms a step with tables for 4,096
+    tokens, 3.4 ms with tables for 131,072).  The logits such a step returns live in the graph's static
+    buffer and are overwritten by the next decode step of the same bucket: consume them (sample, copy)
+    before stepping again.
     """
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: DeviceCacheStorage, *,
@@ -118,7 +122,9 @@ class StepRunner:
         longest = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
         self._graph_widths = [max(1, min(pool.num_pages, -(-longest // manager.page_tokens)))
                               for pool in manager.pools]
-        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graphs: dict[tuple, _DecodeGraph] = {}    # (batch bucket, table widths) -> graph
+        self._graph_pool = None                          # the graphs' intermediates share one memory pool
+        self.last_graph: _DecodeGraph | None = None
         self.graph_replays = 0
 
     # ------------------------------------------------------------------ packing
@@ -273,11 +279,24 @@ class StepRunner:
             b *= 2
         return b
 
+    @staticmethod
+    def width_bucket(pages: int) -> int:
+        """Block-table widths of decode graphs: 1, 2, 3, 4, 6, 8, 12, 16, 24, ... (at most half again what is needed)."""
+        b = 1
+        while b < pages:
+            if b >= 2 and b + b // 2 >= pages:
+                return b + b // 2
+            b *= 2
+        return b
+
     def _decode_step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         size = self.bucket(len(entries))
-        captured = self._graphs.get(size)
+        seqs = self.manager.seqs
+        widths = tuple(min(limit, self.width_bucket(max(len(seqs[e.seq_id].tables[g]) for e in entries)))
+                       for g, limit in enumerate(self._graph_widths))
+        captured = self._graphs.get((size, widths))
         if captured is None:
-            captured = self._capture(entries, size, device_tokens)
+            captured = self._capture(entries, size, list(widths), device_tokens)
         else:
             self._refill(entries, size, captured)
             if device_tokens is not None:
@@ -285,6 +304,7 @@ class StepRunner:
             captured.graph.replay()
             self.model.rt.ops.launches += captured.launches
         self.graph_replays += 1
+        self.last_graph = captured
         wanted = [i for i, e in enumerate(entries) if len(e.want)]
         if len(wanted) == len(entries):
             return captured.logits[:len(entries)]
@@ -337,8 +357,8 @@ class StepRunner:
         captured.index_buffer[:total].copy_(self._staging[:total], non_blocking=True)
         self._staged.record()
 
-    def _capture(self, entries: Sequence[StepEntry], size: int, device_tokens: torch.Tensor | None = None) -> _DecodeGraph:
-        widths = list(self._graph_widths)
+    def _capture(self, entries: Sequence[StepEntry], size: int, widths: list[int],
+                 device_tokens: torch.Tensor | None = None) -> _DecodeGraph:
         probe = self._pack(entries, pad_to=size, widths=widths)
         index_buffer = torch.empty(probe.index_words, dtype=torch.int32, device=self.device)
         ctx = self._pack(entries, pad_to=size, widths=widths, into=index_buffer)
@@ -352,11 +372,13 @@ class StepRunner:
         graph = torch.cuda.CUDAGraph()
         ops = self.model.rt.ops
         before = ops.launches
-        with torch.cuda.graph(graph):
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
             x, residual = self.model.forward(ctx)
             logits = self.model.logits(x, residual, ctx.rows)
         launches = ops.launches - before
         graph.replay()
         captured = _DecodeGraph(graph, index_buffer, logits, widths, launches)
-        self._graphs[size] = captured
+        self._graphs[(size, tuple(widths))] = captured
         return captured
