@@ -267,6 +267,18 @@ def test_decode_graphs_follow_the_longest_request(model_folders, dtype):
             assert runner.graph_replays == steps
     for a, b in zip(outs[True], outs[False]):
         assert torch.equal(a, b)
+    # no more than `max_graphs` graphs are kept: the least recently used one is dropped, and captured again when needed
+    _, manager, storage = build_cache(model, PAGE_B, 40, caching=False)
+    runner = StepRunner(model, manager, storage, cuda_graphs=True, max_model_len=30 * PAGE_B, max_graphs=2)
+    assert manager.admit(0, prompts[1])
+    runner.step([StepEntry(0, prompts[1], [])])
+    manager.commit(0, len(prompts[1]))
+    for t in range(steps):
+        manager.extend(0, [(7 * t + 1) % vocab])
+        again = runner.step([StepEntry(0, [(7 * t + 1) % vocab], [0])]).cpu()
+        manager.commit(0, 1)
+        assert len(runner._graphs) <= 2
+    assert runner.graph_replays == steps
 
 
 def test_multi_turn_replay_reuses_histories_and_changes_no_token(model_folders, tmp_path):

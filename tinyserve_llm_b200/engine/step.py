@@ -104,11 +104,12 @@ class StepRunner:
     would make every step pay for it (64 requests of 512 tokens: 1.26 ms a step with tables for 4,096
     tokens, 3.4 ms with tables for 131,072).  The logits such a step returns live in the graph's static
     buffer and are overwritten by the next decode step of the same bucket: consume them (sample, copy)
-    before stepping again.
+    before stepping again.  At most `max_graphs` graphs are kept; the least recently used one goes first.
     """
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: DeviceCacheStorage, *,
-                 cuda_graphs: bool = True, max_decode_batch: int = 256, max_model_len: int | None = None) -> None:
+                 cuda_graphs: bool = True, max_decode_batch: int = 256, max_model_len: int | None = None,
+                 max_graphs: int = 48) -> None:
         self.model = model
         self.manager = manager
         self.storage = storage
@@ -122,7 +123,8 @@ class StepRunner:
         longest = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
         self._graph_widths = [max(1, min(pool.num_pages, -(-longest // manager.page_tokens)))
                               for pool in manager.pools]
-        self._graphs: dict[tuple, _DecodeGraph] = {}    # (batch bucket, table widths) -> graph
+        self._graphs: dict[tuple, _DecodeGraph] = {}    # (batch bucket, table widths) -> graph, least recently used first
+        self.max_graphs = max_graphs
         self._graph_pool = None                          # the graphs' intermediates share one memory pool
         self.last_graph: _DecodeGraph | None = None
         self.graph_replays = 0
@@ -294,7 +296,9 @@ class StepRunner:
         seqs = self.manager.seqs
         widths = tuple(min(limit, self.width_bucket(max(len(seqs[e.seq_id].tables[g]) for e in entries)))
                        for g, limit in enumerate(self._graph_widths))
-        captured = self._graphs.get((size, widths))
+        captured = self._graphs.pop((size, widths), None)
+        if captured is not None:
+            self._graphs[(size, widths)] = captured          # most recently used last
         if captured is None:
             captured = self._capture(entries, size, list(widths), device_tokens)
         else:
@@ -380,5 +384,7 @@ class StepRunner:
         launches = ops.launches - before
         graph.replay()
         captured = _DecodeGraph(graph, index_buffer, logits, widths, launches)
+        while len(self._graphs) >= self.max_graphs:          # each graph holds a logits buffer of its own
+            self._graphs.pop(next(iter(self._graphs)))
         self._graphs[(size, tuple(widths))] = captured
         return captured
