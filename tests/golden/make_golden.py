@@ -86,4 +86,6 @@ def main(reference_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <folder of tinyserve-llm's source tree>")
+    main(sys.argv[1])
