@@ -234,11 +234,15 @@ struct AttnParams {
 // Address of key (or value) row `key` of kv head `kvh` of the request whose table is given; null if
 // the page was given back.
 template <int HD>
-__device__ __forceinline__ const __nv_bfloat16* kv_row(const __nv_bfloat16* pool, const KVGeometry& geo,
-                                                       const int* table, int kvh, int key) {
-    const int page = table[key / geo.page_tokens];
+__device__ __forceinline__ const __nv_bfloat16* kv_row_of_page(const __nv_bfloat16* pool, const KVGeometry& geo, int page,
+                                                               int kvh, int key) {
     if (page < 0 || page >= geo.num_pages) return nullptr;
     return pool + (long long)page * geo.page_stride + geo.entry_offset + ((long long)kvh * geo.page_tokens + key % geo.page_tokens) * HD;
+}
+template <int HD>
+__device__ __forceinline__ const __nv_bfloat16* kv_row(const __nv_bfloat16* pool, const KVGeometry& geo,
+                                                       const int* table, int kvh, int key) {
+    return kv_row_of_page<HD>(pool, geo, table[key / geo.page_tokens], kvh, key);
 }
 
 // ------------------------------------------------------------------------------------------------ prefill
@@ -345,12 +349,16 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
     // data was written by the host before the step, and the keys and values of earlier steps lie
     // in the pages already; the kernel ahead (rotary + store) writes this step's query and the
     // one new key and value, so only the tile that holds position ctx - 1 is read after the wait.
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // the page of this warp's keys is asked for together with the request's lengths, not after them: which
+    // entry of the table it is follows from the grid alone (the entry is -1, or unused, where the request is shorter)
+    const int key0 = split * SPLIT + warp * DKT;
+    const int page0 = p.block_table[(long long)seq * p.table_width + min(key0 / p.geo.page_tokens, p.table_width - 1)];
     const int q_begin = p.cu_q[seq];
     const bool decoding = p.cu_q[seq + 1] - q_begin == 1;
     const int ctx = p.ctx_lens[seq];
     const int pos = ctx - 1;
     const int g = p.nh / p.nkv;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int first_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int key_begin = split * SPLIT;
     const bool active = decoding && key_begin <= pos && key_begin + SPLIT > first_key;
@@ -370,15 +378,13 @@ __global__ void __launch_bounds__(DW * 32) decode_attention_kernel(AttnParams p)
     __nv_bfloat16* k_tile = q_tile + 16 * HD + warp * 2 * DKT * HD;
     __nv_bfloat16* v_tile = k_tile + DKT * HD;
     const int row_width = (p.nh + 2 * p.nkv) * HD;
-    const int* table = p.block_table + (long long)seq * p.table_width;
-    const int key0 = key_begin + warp * DKT;
     const bool warp_active = key0 <= pos && key0 + DKT > first_key;
     const bool holds_new = warp_active && key0 + DKT > pos;
     const __nv_bfloat16 *k_src = nullptr, *v_src = nullptr;
     int valid = 0;
     if (warp_active) {
-        k_src = kv_row<HD>(p.k_pool, p.geo, table, kvh, key0);
-        v_src = kv_row<HD>(p.v_pool, p.geo, table, kvh, key0);
+        k_src = kv_row_of_page<HD>(p.k_pool, p.geo, page0, kvh, key0);
+        v_src = kv_row_of_page<HD>(p.v_pool, p.geo, page0, kvh, key0);
         valid = k_src ? min(DKT, ctx - key0) : 0;
         if (!holds_new) {
             if (k_src) {
