@@ -59,6 +59,10 @@ MODELS = {
                                              "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}}, 4096),
 }
 FULL_LAYERS = 16
+# One metric, unit and direction for both arms (the driver divides one arm's value by the other's only if
+# these agree); which model's layer sizes were run is in `config`.
+METRIC = "decode tok/s at batch 8 (bf16, one B200)"
+UNIT = "tokens/s"
 BATCH = 8
 CONTEXT = 4096            # benchmark context length of the configuration
 POINT_CONTEXT = 2048      # contexts of the batch 1 / 8 / 64 points
@@ -103,10 +107,17 @@ class ClockSampler:
     def __init__(self) -> None:
         self.rows: list[list[str]] = []
         self.proc = None
+        self.gpu = "0"
+        try:                                  # the process's device 0 need not be the machine's GPU 0: ask by UUID
+            import torch
+            uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+            self.gpu = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:                     # noqa: BLE001
+            pass
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.QUERY}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
@@ -134,14 +145,26 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower() == "active" for r in self.rows)]
         return {"sm_mhz": int(statistics.median(clocks)) if clocks else None,
-                "sm_max_mhz": max(top) if top else None, "reasons": reasons, "samples": len(clocks)}
+                "sm_max_mhz": max(top) if top else None, "reasons": reasons, "samples": len(clocks), "gpu": self.gpu}
+
+
+def size_config(cfg: dict, model_name: str, layers: int, full_layers: int) -> dict:
+    """The keys of `config` both arms share: which model's layer sizes ran, how many layers, batch and context."""
+    return {
+        "model": model_name, "layers": layers, "layers_of_model": full_layers, "hidden_size": cfg["hidden_size"],
+        "intermediate_size": cfg["intermediate_size"], "num_attention_heads": cfg["num_attention_heads"],
+        "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+        "vocab_size": cfg["vocab_size"], "global_batch": BATCH, "seq_len": CONTEXT, "page_tokens": PAGE,
+        "parallelism": "single GPU",
+    }
 
 
 def weight_bytes(cfg: dict, layers: int) -> int:
     h, i, hd = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
     nh, nkv, v = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["vocab_size"]
     per_layer = h * (nh + 2 * nkv) * hd + nh * hd * h + 3 * i * h + 2 * h
-    return 2 * (layers * per_layer + v * h + h)          # lm head (= embedding, tied) read once; rows gathered are noise
+    # the vocabulary projection's matrix is read once, tied or not; the embedding rows a step gathers are noise
+    return 2 * (layers * per_layer + v * h + h)
 
 
 def kv_bytes(cfg: dict, layers: int, batch: int, context: int) -> int:
@@ -321,9 +344,9 @@ def run_ours(args) -> dict:
     achieved = moved / (ms * 1e-3) / 1e9
     flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
     record = {
-        "metric": f"decode tok/s at batch 8 ({model_name}, bf16, one B200)",
+        "metric": METRIC,
         "value": round(value, 1),
-        "unit": "tokens/s",
+        "unit": UNIT,
         "n_gpus": 1,
         "steps": steps,
         "warmup": warmup,
@@ -334,15 +357,10 @@ def run_ours(args) -> dict:
         "dtype": "bf16",
         "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)",
         "impl": "ours",
-        "config": {
-            "model": model_name, "layers": layers, "layers_of_model": full_layers, "hidden_size": cfg["hidden_size"],
-            "intermediate_size": cfg["intermediate_size"], "num_attention_heads": cfg["num_attention_heads"],
-            "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
-            "vocab_size": cfg["vocab_size"], "global_batch": BATCH, "seq_len": CONTEXT,
-            "points_context_len": point_context, "prefill_tokens": PREFILL_TOKENS, "page_tokens": PAGE,
-            "parallelism": "single GPU", "cuda_graphs": bool(graph), "l2": f"inputs larger than L2 (weights {weight_bytes(cfg, layers) / 1e9:.1f} GB per step)",
-            "peaks": peak_kind,
-        },
+        "config": dict(
+            size_config(cfg, model_name, layers, full_layers), points_context_len=point_context,
+            prefill_tokens=PREFILL_TOKENS, cuda_graphs=bool(graph),
+            l2=f"inputs larger than L2 (weights {weight_bytes(cfg, layers) / 1e9:.1f} GB per step)", peaks=peak_kind),
         "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 3), "frac": round(flops / (prefill_ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
@@ -350,7 +368,7 @@ def run_ours(args) -> dict:
         "points": points,
         "mixed": {"decodes": 64, "prefill_tokens": PREFILL_TOKENS, "ms": round(mixed_ms, 3),
                   "value": round((64 + PREFILL_TOKENS) / mixed_ms * 1e3, 1), "unit": "tokens/s"},
-        "e2e": {"value": round(BATCH * steps / e2e_seconds, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+        "e2e": {"value": round(BATCH * steps / e2e_seconds, 1), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": BATCH * 4},
         "gpu_launches": launches,
         "clocks": clocks.summary(),
@@ -394,16 +412,32 @@ def run_reference(args) -> dict:
         value = BATCH * len(decode) / seconds
     except Exception as exc:                                  # noqa: BLE001
         return {"impl": "reference", "unavailable": f"the reference did not run here: {type(exc).__name__}: {exc}"[:300]}
+    return reference_record(value, len(decode), warmup, seconds, layers, clocks.summary())
+
+
+def reference_h2d_bytes(batch: int, context: int) -> int:
+    """
+    Bytes tinyserve-llm copies to the device for one decode step of `batch` requests, counted from
+    the tensors its engine/model_runner.py:73-92 builds: int64 ids, positions, slots and sample rows,
+    float32 temperatures, two int32 offset arrays of batch + 1, and the int32 block tables.
+    """
+    width = -(-(context + 1) // PAGE)
+    return batch * (8 + 8 + 8 + 8 + 4) + 2 * 4 * (batch + 1) + 4 * batch * width
+
+
+def reference_record(value: float, steps: int, warmup: int, seconds: float, layers: int, clocks: dict) -> dict:
+    """The reference arm's line: the same metric, unit and direction as `run_ours` prints."""
     return {
-        "metric": "decode tok/s at batch 8 (Llama 3.2 1B, bf16, one B200)", "value": round(value, 1), "unit": "tokens/s",
-        "n_gpus": 1, "steps": len(decode), "warmup": warmup, "ms_per_step": round(seconds / len(decode) * 1e3, 4),
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT,
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(seconds / max(steps, 1) * 1e3, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)", "impl": "reference",
-        "config": {"model": "Llama-3.2-1B", "layers": layers, "layers_of_model": FULL_LAYERS, "global_batch": BATCH,
-                   "seq_len": CONTEXT, "page_tokens": PAGE, "parallelism": "single GPU",
-                   "timing": "host clock around each decode step of LLM.generate (each ends in a host read)"},
-        "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": BATCH * 8},
-        "clocks": clocks.summary(),
+        "config": dict(size_config(MODEL, MODELS["1b"][0], layers, FULL_LAYERS),
+                       timing="host clock around each decode step of LLM.generate (each ends in a host read)"),
+        "e2e": {"value": round(value, 1), "unit": UNIT, "h2d_bytes_per_step": reference_h2d_bytes(BATCH, CONTEXT),
+                "d2h_bytes_per_step": BATCH * 8,
+                "how": "LLM.generate's own steps: each packs host lists into tensors, copies them and reads the tokens back"},
+        "clocks": clocks,
     }
 
 

@@ -25,6 +25,23 @@ def test_peaks_come_from_the_measured_file_or_the_stated_fallback(tmp_path, monk
     assert kind in ("measured", "fallback") and values["hbm_gbs"] > 1000 and values["bf16_tflops"] > 100
 
 
+def test_both_arms_print_the_same_metric_unit_and_direction():
+    """The driver divides one arm's value by the other's only if these agree; the reference arm's record is built without running it."""
+    sys.path.insert(0, ROOT)
+    import inspect
+
+    import bench
+    ref = bench.reference_record(1000.0, 20, 5, 0.16, 16, {"sm_mhz": 1900})
+    assert ref["metric"] == bench.METRIC and ref["unit"] == bench.UNIT and ref["higher_is_better"] is True
+    assert ref["impl"] == "reference" and ref["e2e"]["unit"] == bench.UNIT
+    assert ref["e2e"]["h2d_bytes_per_step"] > 0 and ref["e2e"]["d2h_bytes_per_step"] > 0
+    assert len(ref["config"]) <= 20 and all(not isinstance(v, (dict, list)) for v in ref["config"].values())
+    ours = inspect.getsource(bench.run_ours)
+    assert '"metric": METRIC' in ours and '"unit": UNIT' in ours and '"higher_is_better": True' in ours
+    shared = bench.size_config(bench.MODEL, "Llama-3.2-1B", 16, 16)
+    assert all(ref["config"][k] == v for k, v in shared.items())
+
+
 @pytest.mark.gpu
 def test_a_short_run_prints_one_record_with_the_contract_keys():
     done = subprocess.run([sys.executable, BENCH, "--layers", "2", "--steps", "5", "--warmup", "3"], capture_output=True, text=True,
@@ -36,6 +53,9 @@ def test_a_short_run_prints_one_record_with_the_contract_keys():
     for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline",
                 "dtype", "data", "config", "prefill", "roofline", "points", "e2e", "gpu_launches", "clocks"):
         assert key in record, key
+    sys.path.insert(0, ROOT)
+    import bench
+    assert record["metric"] == bench.METRIC and record["unit"] == bench.UNIT and record["higher_is_better"] is True
     assert record["n_gpus"] == 1 and record["steps"] == 5 and record["gpu_launches"] > 0
     assert len(record["config"]) <= 20 and all(not isinstance(v, (dict, list)) for v in record["config"].values())
     assert record["config"]["layers"] == 2 and record["config"]["layers_of_model"] == 16
