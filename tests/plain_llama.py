@@ -210,9 +210,14 @@ def hidden_states(cfg: dict, tensors: dict[str, torch.Tensor], ids: list[int], a
 
 
 def logits(cfg: dict, tensors: dict[str, torch.Tensor], ids: list[int], act: str = "float32",
-           run: list[tuple[int, int, bool]] | None = None) -> torch.Tensor:
-    """[T, vocab] float64.  model/llama.py:293-304: lm_head, tied to the embedding when the config says so."""
+           run: list[tuple[int, int, bool]] | None = None, rows: list[int] | None = None) -> torch.Tensor:
+    """
+    [T, vocab] float64 ([len(rows), vocab] with `rows`).  model/llama.py:293-304: lm_head, tied to the
+    embedding when the config says so; engine/model_runner.py:126-127 projects chosen rows only.
+    """
     h = hidden_states(cfg, tensors, ids, act, run)
+    if rows is not None:
+        h = h[torch.tensor(rows, dtype=torch.int64)]
     w = tensors["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else tensors["lm_head.weight"]
     return h @ w.T
 

@@ -12,7 +12,7 @@ import pytest
 import torch
 
 import replay_util as ru
-from tiny_configs import TINY_A, TINY_B, TINY_C, TINY_D
+from tiny_configs import PAGE_A, PAGE_B, TINY_A, TINY_B, TINY_C, TINY_D
 
 pytestmark = pytest.mark.gpu
 
@@ -63,6 +63,40 @@ def test_every_way_of_cutting_gives_the_plain_logits(name, dtype, model_folders,
     want = ru.plain_logits(model_folders[name], {**single, **mixed}, dtype)
     tol = FP32_TOL if dtype == "float32" else bf16_tol(want)
     ru.compare(trace, got, want, **tol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name, page", [("a", PAGE_A), ("b", PAGE_B)])
+def test_cached_prefixes_copies_forks_and_evicted_pages_give_the_plain_logits(name, page, dtype, model_folders, tmp_path):
+    """
+    Prefix reuse on: a request that attaches another's cached pages and copies part of a page, two
+    that compute the same pages in one step (the second switches to the first one's at commit), a
+    fork whose branches write different tokens into the page they share, and a request that comes
+    again after strangers evicted some of its pages.  Every wanted row against the plain logits;
+    the counters show that each path was taken.
+    """
+    trace, requests = ru.cached_paths_trace(RAW[name]["vocab_size"], page)
+    pages = ru.smallest_pool(trace, caching=True) + 4
+    predicted, reused = ru.simulate(trace, pages, caching=True)
+    out = str(tmp_path / "out")
+    got = ru.run_trace(model_folders[name], dtype, trace, out, max_tokens=pages * page, caching=True)
+    stats = ru.read_stats(out)
+    assert stats["partial_copies"] >= 1 and stats["cow_copies"] >= 1 and stats["dedupes"] >= 3 and stats["evictions"] > 0
+    assert stats["reused_tokens"] == sum(reused.values()) > 6 * page
+    for key in ("evictions", "cow_copies", "partial_copies", "publishes", "dedupes"):
+        assert stats[key] == getattr(predicted, key), key
+    want = ru.plain_logits(model_folders[name], requests, dtype)
+    ru.compare(trace, got, want, **(FP32_TOL if dtype == "float32" else bf16_tol(want)))
+
+
+def test_a_fork_without_prefix_reuse_still_shares_and_copies(model_folders, tmp_path):
+    trace, requests = ru.cached_paths_trace(TINY_A["vocab_size"], PAGE_A)
+    pages = ru.smallest_pool(trace, caching=False)
+    out = str(tmp_path / "out")
+    got = ru.run_trace(model_folders["a"], "float32", trace, out, max_tokens=pages * PAGE_A)
+    stats = ru.read_stats(out)
+    assert stats["cow_copies"] == 1 and stats["reused_tokens"] == 0 and stats["publishes"] == 0
+    ru.compare(trace, got, ru.plain_logits(model_folders["a"], requests, "float32"), **FP32_TOL)
 
 
 def _sharp_folder(model_folders, tmp_path, name, factor):

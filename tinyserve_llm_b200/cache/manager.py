@@ -260,8 +260,12 @@ class CacheManager:
         refs = self.pools[0].refs
         return min(match.partial_sources, key=lambda p: (refs[p.page] == 0, p.page))
 
-    def _match(self, tokens: Sequence[int]) -> PrefixMatch:
-        return self.tree.match(tokens) if self.caching else PrefixMatch([])
+    def _match(self, tokens: Sequence[int], reuse_limit: int | None = None) -> PrefixMatch:
+        if not self.caching:
+            return PrefixMatch([])
+        if reuse_limit is not None and reuse_limit < len(tokens) - 1:
+            tokens = tokens[:max(reuse_limit, 0) + 1]      # the walk stops one token short of what it is given
+        return self.tree.match(tokens)
 
     def _cost(self, match: PrefixMatch, source: PageNode | None, num_tokens: int,
               max_new: int | None = None) -> AdmissionCost:
@@ -286,20 +290,24 @@ class CacheManager:
                 costs.append(whole)
         return AdmissionCost(tuple(costs), num_tokens - match.num_tokens)
 
-    def admission_cost(self, tokens: Sequence[int], max_new: int | None = None) -> AdmissionCost:
+    def admission_cost(self, tokens: Sequence[int], max_new: int | None = None,
+                       reuse_limit: int | None = None) -> AdmissionCost:
         """What admitting these tokens would take from the pools and how many tokens it would run.  Read-only."""
-        match = self._match(tokens)
+        match = self._match(tokens, reuse_limit)
         return self._cost(match, self._source(match), len(tokens), max_new)
 
-    def admit(self, seq_id: int, tokens: Sequence[int], max_new: int | None = None) -> bool:
+    def admit(self, seq_id: int, tokens: Sequence[int], max_new: int | None = None,
+              reuse_limit: int | None = None) -> bool:
         """
         Starts a request: attaches its cached prefix, copies a partial match, takes a state slot and
         reserves slots for the next `max_new` tokens after the prefix (None: all the rest).  Returns
         False, changing nothing, if the pools cannot hold the whole request right now.
+        `reuse_limit`: at most this many leading tokens are taken from the cache (a caller that
+        wants the model's output at a prompt position must have that position run).
         """
         assert len(tokens) > 0, "a request needs at least one token"
         assert seq_id not in self.seqs, "the request is admitted already"
-        match = self._match(tokens)
+        match = self._match(tokens, reuse_limit)
         source = self._source(match)
         if not self.fits(self._cost(match, source, len(tokens), max_new).pages_needed):
             return False

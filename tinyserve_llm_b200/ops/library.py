@@ -92,6 +92,7 @@ class Ops:
             fn.restype = _RETURNS[returns]
             fn.argtypes = [_CTYPES[a] for a in arguments]
         self.launches = 0            # kernels of this library launched (or captured into a graph) so far
+        self.calls: dict[str, int] = {}   # calls per exported launcher (and "library_mm": products left to cuBLAS)
         self._error_word: torch.Tensor | None = None
         self.skinny_max_rows = int(self.lib.ts_skinny_linear_max_rows())
         # TINYSERVE_B200_CHAINING=0 launches every kernel fully serialised (no programmatic dependent launch)
@@ -112,6 +113,7 @@ class Ops:
         if getattr(self.lib, name)(*args) != 0:
             raise KernelError(self.lib.ts_last_error().decode())
         self.launches += 1
+        self.calls[name] = self.calls.get(name, 0) + 1
 
     @staticmethod
     def _check(t: torch.Tensor, name: str, dtype: torch.dtype | tuple | None = None, dims: int | None = None) -> None:
@@ -304,7 +306,10 @@ class Ops:
             self._call("ts_skinny_linear", _ptr(weight), _ptr(x), _ptr(out), c_int(x.shape[0]), c_int(weight.shape[0]),
                        c_int(x.shape[1]), c_longlong(x.shape[1]), c_longlong(weight.shape[0]), c_int(0),
                        c_int(_DTYPE_CODE[out_dtype]), _stream())
+            if out_dtype == torch.float32:
+                self.calls["ts_skinny_linear:float32_out"] = self.calls.get("ts_skinny_linear:float32_out", 0) + 1
             return out
+        self.calls["library_mm"] = self.calls.get("library_mm", 0) + 1
         if out_dtype != x.dtype:
             return torch.mm(x, weight.t(), out_dtype=out_dtype)
         return torch.mm(x, weight.t())
