@@ -12,6 +12,16 @@ with tinyserve-llm's loader into its LlamaForCausalLM (float32, CPU), and stores
   golden_<name>_logits.npy    float32 logits [rows kept, vocab] of the probe sequence, computed with
                               tinyserve-llm's DenseCausalAttention oracle (whole sequence, no cache)
 
+and, once,
+
+  golden_parts_bf16.npz       what tinyserve-llm's own modules (RMSNorm with and without residual,
+                              SiluAndMul, apply_rotary_emb) give in bfloat16 on the CPU for seeded
+                              bfloat16 inputs: the places where its bfloat16 model rounds.  Logits of
+                              a whole bfloat16 model cannot pin those places (one-ulp flips spread
+                              chaotically through the layers: the plain float32 logits are as close
+                              to tinyserve-llm's bfloat16 logits as the plain bfloat16 ones are), so
+                              the parts are held to them one by one, bit for bit.
+
 Nothing of tinyserve-llm is copied: it is imported, run once, and its small outputs are kept.
 """
 
@@ -85,7 +95,39 @@ def main(reference_root: str) -> None:
             print(name, "logits", tuple(logits[rows].shape), "greedy", record["greedy"])
 
 
+def parts_bf16(reference_root: str) -> None:
+    sys.path.insert(0, reference_root)
+    os.environ["TINYSERVE_COMPILE"] = "0"
+    from tinyserve_llm.model.llama import RMSNorm, SiluAndMul, apply_rotary_emb
+
+    g = torch.Generator().manual_seed(2024)
+    bf = torch.bfloat16
+    rows, hidden, inter, heads, hd = 6, 80, 48, 3, 16
+    x = (3.0 * torch.randn(rows, hidden, generator=g)).to(bf)
+    residual = (3.0 * torch.randn(rows, hidden, generator=g)).to(bf)
+    weight = (1.0 + 0.25 * torch.randn(hidden, generator=g)).to(bf)
+    gate_up = (2.0 * torch.randn(rows, 2 * inter, generator=g)).to(bf)
+    q = torch.randn(rows, heads, hd, generator=g).to(bf)
+    angles = torch.rand(rows, 1, hd // 2, generator=g) * 50.0
+    cos, sin = angles.cos(), angles.sin()
+    eps = 1e-5
+    norm = RMSNorm(hidden, eps).to(bf)
+    with torch.no_grad():
+        norm.weight.copy_(weight)
+        plain_norm = norm(x)
+        added, carried = norm(x, residual)
+        act = SiluAndMul()(gate_up)
+        rotated = apply_rotary_emb(q, cos, sin)
+    as32 = lambda t: t.float().numpy()       # noqa: E731  (bfloat16 values are exact in float32)
+    np.savez(os.path.join(HERE, "golden_parts_bf16.npz"), eps=np.float64(eps), x=as32(x), residual=as32(residual),
+             weight=as32(weight), rms_norm=as32(plain_norm), add_rms_norm=as32(added), carried=as32(carried),
+             gate_up=as32(gate_up), swiglu=as32(act), q=as32(q), cos=cos.numpy(), sin=sin.numpy(),
+             rotated=as32(rotated))
+    print("parts in bfloat16 written")
+
+
 if __name__ == "__main__":
     if len(sys.argv) != 2:
         sys.exit("usage: make_golden.py <folder of tinyserve-llm's source tree>")
     main(sys.argv[1])
+    parts_bf16(sys.argv[1])

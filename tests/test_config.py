@@ -79,3 +79,25 @@ def test_to_dict_round_trip():
     for raw in (TINY_A, TINY_B, TINY_C):
         cfg = LlamaConfig.from_dict(raw)
         assert LlamaConfig.from_dict(cfg.to_dict()) == cfg
+
+
+def test_pages_that_fit_is_the_share_less_everything_else_in_whole_pages():
+    from tinyserve_llm_b200.engine.llm import pages_that_fit
+    gib = 1 << 30
+    # 180 GiB device, 10 GiB in use (weights), 90 % share, 2 GiB step peak, 1 GiB held by graphs, 8 MiB pages
+    assert pages_that_fit(180 * gib, 170 * gib, 0.9, 2 * gib, 1 * gib, 8 << 20) == int((162 - 10 - 2 - 1) * 128)
+    assert pages_that_fit(180 * gib, 170 * gib, 0.9, 2 * gib, 0, 8 << 20) == pages_that_fit(180 * gib, 170 * gib, 0.9, 2 * gib, 1 * gib, 8 << 20) + 128
+    assert pages_that_fit(80 * gib, 8 * gib, 0.9, gib, gib, 8 << 20) < 0          # already over the share: the engine raises
+    assert pages_that_fit(gib, gib, 0.5, 0, 0, 3 * (1 << 20)) == 170              # whole pages only
+
+
+def test_a_head_size_no_kernel_takes_is_refused_when_the_model_is_described():
+    """config.json may state any even head_dim; the attention part takes multiples of 16 up to 256 and says so at once."""
+    from tiny_configs import TINY_B
+    from tinyserve_llm_b200.config.llama import LlamaConfig, llama_model_spec
+    from tinyserve_llm_b200.parts.model import declared_tensors
+    for bad in (24, 272):
+        spec = llama_model_spec(LlamaConfig.from_dict(dict(TINY_B, head_dim=bad)))
+        with pytest.raises(ValueError, match=f"head_dim={bad}"):
+            declared_tensors(spec)
+    declared_tensors(llama_model_spec(LlamaConfig.from_dict(dict(TINY_B, head_dim=48))))

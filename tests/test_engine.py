@@ -13,7 +13,7 @@ import torch
 
 import plain_llama as plain
 import replay_util as ru
-from tiny_configs import PAGE_A, PAGE_B, TINY_A, TINY_B
+from tiny_configs import PAGE_A, PAGE_B, TINY_A, TINY_B, TINY_D
 
 pytestmark = pytest.mark.gpu
 
@@ -167,13 +167,46 @@ def test_step_records_and_requests_the_engine_refuses(model_folders):
         make_llm(model_folders["a"], PAGE_A, max_model_len=100000, max_num_batched_tokens=200000)
 
 
-def test_cache_sized_from_free_memory_and_random_weights_from_a_seed(model_folders):
+def test_cache_sized_from_free_memory_and_random_weights_from_a_seed(model_folders, tmp_path):
     from tinyserve_llm_b200 import LLM, CacheConfig, SchedulerConfig
+    from tinyserve_llm_b200.weights import write_random_model
     llm = LLM(model_folders["a"], SchedulerConfig(max_model_len=128, max_num_seqs=4, max_num_batched_tokens=128),
               CacheConfig(block_size=PAGE_A), dtype="bfloat16", gpu_memory_utilization=0.05, random_weights_seed=3)
     assert llm.cache.num_pages > 100
     out = llm.generate([[5, 6, 7]], greedy(4))
     assert len(out[0].token_ids[0]) == 4 and llm.cache.stats().pages_in_use == 0
+    # one seed, one model: the folder written from the same seed holds the same weights
+    folder = str(tmp_path / "seed3")
+    write_random_model(folder, TINY_A, 3)
+    written = LLM(folder, SchedulerConfig(max_model_len=128, max_num_seqs=4, max_num_batched_tokens=128),
+                  CacheConfig(block_size=PAGE_A), dtype="bfloat16", num_blocks=16)
+    assert torch.equal(written.model.embedding, llm.model.embedding)
+    assert torch.equal(written.model.blocks[1].mixer.qkv.weight, llm.model.blocks[1].mixer.qkv.weight)
+    assert written.generate([[5, 6, 7]], greedy(4))[0].token_ids == out[0].token_ids
+
+
+def test_a_cache_sized_from_free_memory_leaves_room_for_the_widest_steps(model_folders):
+    """
+    `num_blocks=None` with 64 sequence slots: 64 requests decode across several buckets of batch size
+    and table width (their lengths differ, they finish one after another), with logits of 64 rows
+    and graphs of several shapes alive; the memory torch holds never passes the share it was given.
+    """
+    from tinyserve_llm_b200 import LLM, CacheConfig, SchedulerConfig
+    share = 0.04
+    total = torch.cuda.mem_get_info()[1]
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats()
+    llm = LLM(model_folders["d"], SchedulerConfig(max_model_len=1000, max_num_seqs=64, max_num_batched_tokens=2048,
+                                                   eos_token_id=-2, prefill_chunk=256),
+              CacheConfig(block_size=64), dtype="bfloat16", gpu_memory_utilization=share, seed=1)
+    vocab = TINY_D["vocab_size"]
+    prompts = [ru.random_ids(vocab, 5 + 11 * i, 300 + i) for i in range(64)]
+    params = [greedy(20 + 3 * (i % 9)) for i in range(64)]
+    out = llm.generate(prompts, params)
+    assert [len(c.token_ids[0]) for c in out] == [p.max_tokens for p in params]
+    assert llm.runner.graph_replays > 20 and len(llm.runner._graphs) >= 3
+    assert torch.cuda.max_memory_allocated() <= share * total
+    assert llm.cache.stats().pages_in_use == 0
 
 
 def test_command_line_writes_one_json_record(model_folders, tmp_path):

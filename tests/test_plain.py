@@ -71,3 +71,28 @@ def test_window_masks_far_keys():
     assert not torch.allclose(full[5:], win[5:])
     short = plain.causal_attention(q[2:5], k[2:5], v[2:5], 0.5, "float32")
     torch.testing.assert_close(win[4], short[2])           # query 4 with window 3 sees keys 2, 3, 4
+
+
+def test_bfloat16_rounding_places_are_those_of_the_reference_parts():
+    """
+    Where the plain implementation rounds in bfloat16 mode, against what tinyserve-llm's own modules
+    gave in bfloat16 for the same inputs (golden_parts_bf16.npz), bit for bit: the norm rounds before
+    the weight multiplies and carries the rounded sum, silu is rounded before it multiplies, the
+    rotation is rounded once.
+    """
+    g = np.load(os.path.join(GOLDEN, "golden_parts_bf16.npz"))
+    t = lambda key: torch.from_numpy(g[key]).to(plain.F64)       # noqa: E731
+    eps = float(g["eps"])
+    assert torch.equal(plain.rms_norm(t("x"), t("weight"), eps, "bfloat16"), t("rms_norm"))
+    normed, carried = plain.add_rms_norm(t("x"), t("residual"), t("weight"), eps, "bfloat16")
+    assert torch.equal(normed, t("add_rms_norm")) and torch.equal(carried, t("carried"))
+    assert torch.equal(plain.swiglu(t("gate_up"), "bfloat16"), t("swiglu"))
+    cos, sin = t("cos")[:, 0, :], t("sin")[:, 0, :]
+    assert torch.equal(plain.rotate_half(t("q"), cos, sin, "bfloat16"), t("rotated"))
+    # the test has teeth: a rounding moved by one place changes some element
+    unrounded_silu = plain.rnd(t("gate_up").chunk(2, -1)[0] * torch.sigmoid(t("gate_up").chunk(2, -1)[0])
+                               * t("gate_up").chunk(2, -1)[1], "bfloat16")
+    assert not torch.equal(unrounded_silu, t("swiglu"))
+    s = t("x") + t("residual")
+    late = plain.rnd(s * torch.rsqrt(s.pow(2).mean(-1, keepdim=True) + eps) * t("weight"), "bfloat16")
+    assert not torch.equal(late, t("add_rms_norm"))

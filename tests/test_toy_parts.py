@@ -420,3 +420,98 @@ def test_toy_routed_feed_forward_and_toy_position_encoding_are_registered_built_
     torch.testing.assert_close(torch.cat(got_b), plain_logits(b), atol=3e-5, rtol=1e-5)
     manager.release("a"), manager.release("b")
     assert manager.stats().pages_in_use == 0
+
+
+def test_a_toy_norm_brings_a_cuda_kernel_of_its_own():
+    """
+    A toy norm whose arithmetic runs in a CUDA kernel that lives beside this test (tests/toy_kernels.cu),
+    not in the framework: the part compiles it as an extension of the kernel library, registers its
+    launcher and calls it through `Ops.call`; it is graph safe, so decode steps of the model built
+    from it are replayed from CUDA graphs.  No file of the framework names the kernel.
+    """
+    import os
+
+    import plain_llama as plain
+    from tinyserve_llm_b200.config.spec import (AttentionSpec, BlockSpec, GatedMLPSpec, ModelSpec, PartSpec,
+                                                RMSNormSpec, RotarySpec, RunEntry)
+    from tinyserve_llm_b200.engine.loading import build_cache
+    from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
+    from tinyserve_llm_b200.ops import KernelError, get_ops
+    from tinyserve_llm_b200.parts.base import Norm, Runtime, TensorDecl, register_part
+    from tinyserve_llm_b200.parts.model import DecoderModel, declared_tensors
+    from tinyserve_llm_b200.weights import random_tensors
+
+    hidden, heads, kv, hd, inter, vocab, shift = 64, 4, 2, 16, 48, 97, 0.125
+    source = os.path.join(os.path.dirname(os.path.abspath(__file__)), "toy_kernels.cu")
+
+    @dataclass(frozen=True)
+    class GainSpec(PartSpec):
+        kind: str = field(init=False, default="toy_gain")
+        size: int = 0
+        shift: float = 0.0
+
+    @register_part("norm", "toy_gain")
+    class GainNorm(Norm):
+        """(x + residual) * gain + shift, no statistics: the sum is the new residual stream."""
+
+        graph_safe = True
+
+        @classmethod
+        def declare(cls, spec):
+            return {"gain": TensorDecl((spec.size,), init="unit")}
+
+        def __init__(self, spec, tensors, rt):
+            super().__init__(spec, tensors, rt)
+            self.gain = tensors["gain"].to(rt.device, torch.float32).contiguous()
+            rt.ops.load_extension("toy", [source], {"toy_gain": ("int", "ppfpiip")})
+
+        def forward(self, x, residual, rows=None):
+            s = x if residual is None else x + residual
+            picked = s if rows is None else s.index_select(0, rows.long())
+            out = torch.empty_like(picked)
+            self.rt.ops.call("toy_gain", picked.data_ptr(), self.gain.data_ptr(), self.spec.shift, out.data_ptr(),
+                             picked.shape[0], picked.shape[1], self.rt.ops.stream())
+            return out, s
+
+    rotary = RotarySpec(head_dim=hd, theta=1000.0, max_positions=128)
+    attn = AttentionSpec(hidden_size=hidden, num_heads=heads, num_kv_heads=kv, head_dim=hd, scale=hd ** -0.5, position=rotary)
+    mlp, rms = GatedMLPSpec(hidden_size=hidden, intermediate_size=inter), RMSNormSpec(size=hidden, eps=1e-5)
+    gain = GainSpec(size=hidden, shift=shift)
+    blocks = (BlockSpec("pre_norm", attn, mlp, rms, gain, prefix="layers.0."),)
+    spec = ModelSpec("ToyGain", vocab, hidden, blocks, (RunEntry(0, 0),), rms, "embed.weight", "final_norm.", None, 128, -1)
+    tensors = dict(random_tensors(declared_tensors(spec), 13, std=0.1, unit_std=0.2))
+    device = torch.device("cuda", torch.cuda.current_device())
+    ops = get_ops()
+    model = DecoderModel(spec, {k: v.to(device) for k, v in tensors.items()}, Runtime(dtype=torch.float32, device=device, ops=ops))
+    assert model.graph_safe and ops.calls.get("toy_gain", 0) == 0
+    _, manager, storage = build_cache(model, 16, 8)
+    runner = StepRunner(model, manager, storage)
+
+    def plain_logits(ids):
+        w = {k: v.double() for k, v in tensors.items()}
+        lw = {k[len("layers.0."):]: v for k, v in w.items() if k.startswith("layers.0.")}
+        cfg = {"num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd, "hidden_size": hidden,
+               "rope_theta": 1000.0, "max_position_embeddings": 128}
+        x = w["embed.weight"][torch.tensor(ids)]
+        n, residual = plain.rms_norm(x, lw["input_layernorm.weight"], 1e-5, "float32"), x
+        a, _ = plain.attention_block(cfg, lw, n, torch.arange(len(ids)), "float32")
+        residual = a + residual
+        x = plain.mlp_block(lw, residual * lw["post_attention_layernorm.gain"] + shift, "float32")
+        return plain.add_rms_norm(x, residual, w["final_norm.weight"], 1e-5, "float32")[0] @ w["embed.weight"].T
+
+    ids = torch.randint(0, vocab, (40,), generator=torch.Generator().manual_seed(3)).tolist()
+    got = []
+    assert manager.admit("r", ids[:25])
+    got.append(runner.step([StepEntry("r", ids[:25], list(range(25)))]).cpu().double())
+    manager.commit("r", 25)
+    for t in ids[25:]:                                              # token by token: replayed from a CUDA graph
+        manager.extend("r", [t])
+        got.append(runner.step([StepEntry("r", [t], [0])]).cpu().double().clone())
+        manager.commit("r", 1)
+    torch.testing.assert_close(torch.cat(got), plain_logits(ids), atol=3e-5, rtol=1e-5)
+    assert runner.graph_replays == 15 and ops.calls["toy_gain"] >= 2
+    with pytest.raises(KernelError, match="toy_gain: bad sizes"):   # the extension reports errors like the library does
+        ops.call("toy_gain", 0, 0, 0.0, 0, 1, 0, ops.stream())
+    with pytest.raises(KernelError, match="not a registered kernel"):
+        ops.call("toy_unknown", 0)
+    manager.release("r")

@@ -10,7 +10,7 @@ from safetensors.torch import save_file
 
 from tiny_configs import SEED_A, TINY_A, TINY_B, WEIGHTS
 from tinyserve_llm_b200.config import LlamaConfig, llama_model_spec
-from tinyserve_llm_b200.parts.model import declared_tensors, optional_tensors
+from tinyserve_llm_b200.parts.model import declared_tensors
 from tinyserve_llm_b200.weights import (CheckpointError, SafetensorsError, SafetensorsFile, load_tensors,
                                         random_tensors, write_random_model, write_safetensors)
 
@@ -41,7 +41,7 @@ def test_random_model_loads_and_keeps_stored_dtypes(tmp_path):
     write_random_model(folder, TINY_A, SEED_A, **WEIGHTS)
     assert json.load(open(os.path.join(folder, "config.json"))) == TINY_A
     spec, declared = _declared(TINY_A)
-    tensors = load_tensors(folder, declared, optional=optional_tensors(spec))
+    tensors = load_tensors(folder, declared, optional=spec.optional_tensors, ignored_suffixes=spec.ignored_suffixes)
     assert set(tensors) == set(declared)
     assert all(t.dtype == torch.bfloat16 for t in tensors.values())
     write_random_model(folder, TINY_A, SEED_A, store_dtype="float32", **WEIGHTS)
@@ -73,7 +73,7 @@ def test_integer_tables_become_int32_and_sharded_checkpoints_load(tmp_path):
     second["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)     # old checkpoints carry it: skipped
     second["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()    # tied copy: accepted and dropped
     save_file(second, str(tmp_path / "model-00002-of-00002.safetensors"))
-    loaded = load_tensors(str(tmp_path), declared, optional=optional_tensors(spec))
+    loaded = load_tensors(str(tmp_path), declared, optional=spec.optional_tensors, ignored_suffixes=spec.ignored_suffixes)
     assert all(torch.equal(loaded[k], tensors[k]) for k in tensors)
     from tinyserve_llm_b200.parts.base import TensorDecl
     save_file({"table": torch.arange(6, dtype=torch.int64).reshape(2, 3)}, str(tmp_path / "model.safetensors"))
@@ -92,7 +92,7 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     tensors["model.layers.0.self_attn.q_proj.bias"] = torch.zeros(2)
     save_file(tensors, str(tmp_path / "model.safetensors"))
     with pytest.raises(CheckpointError) as err:
-        load_tensors(str(tmp_path), declared, optional=optional_tensors(spec))
+        load_tensors(str(tmp_path), declared, optional=spec.optional_tensors, ignored_suffixes=spec.ignored_suffixes)
     e = err.value
     assert e.missing == ["model.layers.1.mlp.up_proj.weight", "lm_head.weight"]
     assert e.unexpected == ["model.layers.0.self_attn.q_proj.bias", "model.layers.9.mlp.down_proj.weight"]
@@ -108,7 +108,7 @@ def test_untied_model_does_not_accept_a_missing_head(tmp_path):
     del tensors["lm_head.weight"]
     save_file(tensors, str(tmp_path / "model.safetensors"))
     with pytest.raises(CheckpointError, match="lm_head.weight"):
-        load_tensors(str(tmp_path), declared, optional=optional_tensors(spec))
+        load_tensors(str(tmp_path), declared, optional=spec.optional_tensors, ignored_suffixes=spec.ignored_suffixes)
 
 
 def test_no_files_and_truncated_files(tmp_path):

@@ -223,4 +223,8 @@ def llama_model_spec(config: LlamaConfig) -> ModelSpec:
         lm_head_name=None if config.tie_word_embeddings else "lm_head.weight",
         max_positions=config.max_position_embeddings,
         eos_token_id=config.eos_token_id,
+        # model/loader.py:19, 43-47 of the reference: a tied checkpoint may still carry lm_head.weight, and
+        # checkpoints of older exporters carry each layer's rotary inv_freq buffer
+        optional_tensors=("lm_head.weight",) if config.tie_word_embeddings else (),
+        ignored_suffixes=("rotary_emb.inv_freq",),
     )

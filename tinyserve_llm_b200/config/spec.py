@@ -120,6 +120,8 @@ class ModelSpec:
     lm_head_name: str | None         # None: tied to the embedding
     max_positions: int
     eos_token_id: int
+    optional_tensors: tuple[str, ...] = ()     # names a checkpoint may carry that the model does not read
+    ignored_suffixes: tuple[str, ...] = ()     # tensors whose names end so are skipped (buffers the model recomputes)
     extras: dict[str, Any] = field(default_factory=dict, compare=False)
 
     @property

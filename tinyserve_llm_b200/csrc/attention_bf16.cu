@@ -18,19 +18,15 @@
 //
 // Keys and values beyond the request's length (the unwritten tail of its last page) are zero-filled
 // on load and masked by select, so whatever those slots hold never reaches a result.
+#include "attention_bf16.h"
+
 #include "common.cuh"
 
 namespace {
 
 constexpr int TILE = 64;           // keys per tile, queries per prefill CTA
-#ifndef TS_DECODE_WARPS
-#define TS_DECODE_WARPS 4
-#endif
-#ifndef TS_DECODE_TILE
-#define TS_DECODE_TILE 64
-#endif
-constexpr int DW = TS_DECODE_WARPS;  // warps of a decode CTA, one tile of DKT keys each
-constexpr int DKT = TS_DECODE_TILE;  // keys per warp of a decode CTA: small tiles, many warps, to hide the tile routine's latencies
+constexpr int DW = 4;              // warps of a decode CTA, one tile of DKT keys each
+constexpr int DKT = 64;            // keys per warp of a decode CTA
 constexpr int SPLIT = DW * DKT;     // keys per decode split
 static_assert(DKT % 16 == 0 && TILE % DKT == 0, "a decode tile is a multiple of 16 keys and divides a prefill tile (and so a page)");
 constexpr float LOG2E = 1.4426950408889634f;
@@ -592,11 +588,8 @@ TS_API int ts_attention_bf16_supported(int hd, int page_tokens, int nh, int nkv)
     return (hd == 64 || hd == 128) && page_tokens % TILE == 0 && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16;
 }
 
-// max_q_len / min_q_len: longest and shortest number of tokens a request feeds in this step (which
-// kernels run); max_ctx_len: an upper bound of the requests' lengths (the decode grid and scratch).
-// prefill_seqs (optional, device): the requests that feed more than one token, so that the prefill
-// grid has no CTAs for the others (a CTA that only finds out it has nothing to do still holds its
-// shared memory while it does).
+// The arguments are described in attention_bf16.h.  (A prefill CTA that only finds out it has nothing
+// to do still holds its shared memory while it does: hence prefill_seqs.)
 TS_API int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_pool, const void* v_pool,
                                    long long page_stride, long long entry_offset, int page_tokens, int num_pages,
                                    const int* block_table, int table_width, const int* cu_q, const int* ctx_lens,

@@ -5,19 +5,12 @@
 
 #include <mutex>
 
+#include "attention_bf16.h"
 #include "common.cuh"
 
 // Partial outputs and (max, sum) pairs of the decode splits.  In host code this name is only a
 // handle for cudaGetSymbolAddress, never a device address.
 static __device__ __align__(256) float g_decode_scratch[TS_NOALLOC_SCRATCH_FLOATS];
-
-extern "C" long long ts_attention_bf16_scratch_floats(int num_seqs, int nh, int hd, int max_ctx_len);
-extern "C" int ts_paged_attention_bf16(const void* qkv, void* out, const void* k_pool, const void* v_pool,
-                                       long long page_stride, long long entry_offset, int page_tokens, int num_pages,
-                                       const int* block_table, int table_width, const int* cu_q, const int* ctx_lens,
-                                       int num_seqs, int max_q_len, int min_q_len, int max_ctx_len, int nh, int nkv,
-                                       int hd, float scale, int window, float* scratch, long long scratch_floats,
-                                       const int* prefill_seqs, int num_prefill_seqs, cudaStream_t stream);
 
 namespace {
 

@@ -16,7 +16,9 @@
  *
  *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
  *    that device current) and keeps it.  Make that first call on each device once at start-up,
- *    outside any stream capture.
+ *    outside any stream capture.  The address is good for as long as the device's context lives:
+ *    a host that tears the context down (cudaDeviceReset) must not call this again afterwards in
+ *    the same process.
  *  - The function itself calls no cudaMalloc, cudaFree or other allocating routine.
  *  - All calls on a device share the one array.  Its contents are whatever the last call left; the
  *    kernels write every partial result they later read, so nothing has to be cleared between
@@ -35,6 +37,10 @@
 #ifdef __cplusplus
 extern "C" {
 #endif
+
+/* Floats the built-in scratch holds (TS_NOALLOC_SCRATCH_FLOATS): compare with
+ * ts_attention_bf16_scratch_floats(requests, heads, head size, longest context) before relying on this entry point. */
+long long ts_decode_attention_noalloc_max_floats(void);
 
 int ts_decode_attention_bf16_noalloc(const void* qkv, void* out, const void* k_pool, const void* v_pool,
                                      long long page_stride, long long entry_offset, int page_tokens, int num_pages,

@@ -30,16 +30,13 @@
 
 namespace {
 
-#ifndef TS_FLASH_KEYS
-#define TS_FLASH_KEYS 128
-#endif
 constexpr int QROWS = 128;                   // queries per CTA
 constexpr int TMEM_COLS = 256;
 // Sizes that follow from the head size.  A tile row of more than 64 dims lies in shared memory as
 // sub-tiles of 64 dims (128 bytes, the widest row the 128-byte swizzle takes), one after the other.
 template <int HD>
 struct Shape {
-    static constexpr int KEYS = HD == 64 ? TS_FLASH_KEYS : 64;     // keys per tile: two CTAs must fit an SM
+    static constexpr int KEYS = HD == 64 ? 128 : 64;     // keys per tile: two CTAs must fit an SM
     static constexpr int SUBS = HD / 64;                           // sub-tiles of 64 dims
     static constexpr int SUB_Q = QROWS * 128, SUB_KV = KEYS * 128; // bytes of a sub-tile
     static constexpr int Q_BYTES = QROWS * HD * 2, KV_BYTES = KEYS * HD * 2, STAGE_BYTES = 2 * KV_BYTES;

@@ -36,6 +36,16 @@ class CacheConfig:
     device: str = "cuda"
 
 
+def pages_that_fit(total: int, free: int, utilisation: float, step_peak: int, graphs_held: int, bytes_per_page: int) -> int:
+    """
+    Pages the pool may have: `utilisation` x the device's memory, less what is in use already (the
+    weights, other processes), less the largest step's activations, less what decode graphs keep
+    for good, in whole pages.  Zero or less means the engine does not fit.
+    """
+    budget = total * utilisation - (total - free) - step_peak - graphs_held
+    return int(budget // max(bytes_per_page, 1))
+
+
 @dataclass
 class StepRecord:
     """One engine step; the two stats are running totals (subtract consecutive records)."""
@@ -109,7 +119,7 @@ class LLM:
         needs_state = any(state for _, state in self.model.cache_needs())
         state_slots = scheduler_config.max_num_seqs if needs_state else 0
         if num_blocks is None:
-            num_blocks = self._size_cache(gpu_memory_utilization, state_slots)
+            num_blocks = self._size_cache(gpu_memory_utilization, state_slots, cuda_graphs)
         self.layout, self.cache, self.storage = build_cache(
             self.model, cache_config.block_size, num_blocks, caching=cache_config.caching, num_state_slots=state_slots)
         self.scheduler = Scheduler(scheduler_config, self.cache)
@@ -129,32 +139,64 @@ class LLM:
             return int(self.tokenizer.eos_token_id)
         return self.model.spec.eos_token_id
 
-    def _size_cache(self, utilisation: float, state_slots: int) -> int:
-        """Runs one worst-case step on a throwaway cache, then gives the pool what is left under the limit."""
+    def _size_cache(self, utilisation: float, state_slots: int, cuda_graphs: bool) -> int:
+        """
+        Measures what the engine itself will need at its worst and gives the page pool the rest of
+        `utilisation` x the device's memory.  tinyserve-llm warms up with the token budget spread
+        over as many sequences as the cap allows, every one sampling, so that the [rows, vocab]
+        logits and the sampler's buffers are in the measured peak (engine/llm_engine.py:112-140).
+        The same step runs here, on a throwaway pool.  Then, where decode steps will be replayed
+        from CUDA graphs, the widest one the configuration allows (every sequence slot taken, block
+        tables for `max_model_len`) is captured once: what the graphs hold (their shared logits
+        buffer and their memory pool, which the widest graph sizes) stays allocated beside every
+        later step.
+        """
         cfg, page = self.scheduler_config, self.cache_config.block_size
-        tokens = min(cfg.max_num_batched_tokens, cfg.max_model_len - 1)
-        if cfg.prefill_chunk:
-            tokens = min(tokens, cfg.prefill_chunk)
-        pages = -(-tokens // page) + 1
+        device = self.device
+        seqs = min(cfg.max_num_seqs, cfg.max_num_batched_tokens)
+        each = max(1, min(cfg.max_num_batched_tokens // seqs, cfg.max_model_len - 1, cfg.prefill_chunk or (1 << 30)))
+        pages = seqs * -(-(each + 1) // page) + 1
         _, manager, storage = build_cache(self.model, page, pages, caching=False, num_state_slots=max(state_slots, 1))
-        runner = StepRunner(self.model, manager, storage, cuda_graphs=False)
-        torch.cuda.synchronize(self.device)
-        torch.cuda.reset_peak_memory_stats(self.device)
-        baseline = torch.cuda.memory_allocated(self.device)
-        manager.admit(0, [0] * tokens)
-        runner.step([StepEntry(0, [0] * tokens, [tokens - 1])])
-        torch.cuda.synchronize(self.device)
-        peak = torch.cuda.max_memory_allocated(self.device) - baseline
-        del runner, manager, storage
+        eager = StepRunner(self.model, manager, storage, cuda_graphs=False)
+        sampler = Sampler(self.model.rt.ops, device, 0)
+        torch.cuda.synchronize(device)
+        torch.cuda.reset_peak_memory_stats(device)
+        baseline = torch.cuda.memory_allocated(device)
+        entries = [StepEntry(i, [0] * each, [each - 1]) for i in range(seqs)]
+        for e in entries:
+            manager.admit(e.seq_id, e.tokens)
+        logits = eager.step(entries)
+        sampler.sample_async(logits, [1.0] * seqs, [(i, 0, 0) for i in range(seqs)]).wait()
+        torch.cuda.synchronize(device)
+        step_peak = torch.cuda.max_memory_allocated(device) - baseline
+        del logits, eager, sampler
+        graphs_held = 0
+        if cuda_graphs and self.model.graph_safe:
+            torch.cuda.empty_cache()
+            before = torch.cuda.memory_reserved(device)
+            widest = [-(-cfg.max_model_len // page)] * len(manager.pools)
+            replayed = StepRunner(self.model, manager, storage, max_model_len=cfg.max_model_len,
+                                  max_decode_batch=cfg.max_num_seqs, table_pages=widest)
+            for e in entries:
+                manager.commit(e.seq_id, each)
+                manager.extend(e.seq_id, [0])
+            replayed._capture([StepEntry(i, [0], [0]) for i in range(seqs)], StepRunner.bucket(seqs),
+                              list(replayed._graph_widths))
+            torch.cuda.synchronize(device)
+            torch.cuda.empty_cache()             # what the capture's eager run cached goes; what the graphs hold stays
+            graphs_held = max(0, torch.cuda.memory_reserved(device) - before)
+            del replayed
+        del manager, storage, entries
         torch.cuda.empty_cache()
-        free, total = torch.cuda.mem_get_info(self.device)
+        free, total = torch.cuda.mem_get_info(device)
         layout = plan_layout(self.model.cache_needs(), page)
         per_page = sum(DeviceCacheStorage.bytes_per_page(layout, self.dtype))
-        budget = total * utilisation - (total - free) - peak
-        num_blocks = int(budget // max(per_page, 1))
-        logger.info("warm-up: %d tokens, peak activations %.2f GiB", tokens, peak / 2 ** 30)
+        num_blocks = pages_that_fit(total, free, utilisation, step_peak, graphs_held, per_page)
+        logger.info("warm-up: %d sequences of %d tokens, step peak %.2f GiB, decode graphs hold %.2f GiB", seqs, each,
+                    step_peak / 2 ** 30, graphs_held / 2 ** 30)
         if num_blocks <= 0:
-            raise RuntimeError("no memory left for the cache; lower max_num_batched_tokens or raise gpu_memory_utilization")
+            raise RuntimeError("no memory left for the cache; lower max_num_batched_tokens or max_num_seqs, or raise "
+                               "gpu_memory_utilization")
         return num_blocks
 
     # ------------------------------------------------------------------ the loop

@@ -15,7 +15,7 @@ from tinyserve_llm_b200.cache.storage import DeviceCacheStorage
 from tinyserve_llm_b200.config.registry import load_model_spec
 from tinyserve_llm_b200.ops import get_ops
 from tinyserve_llm_b200.parts.base import Runtime
-from tinyserve_llm_b200.parts.model import DecoderModel, declared_tensors, optional_tensors
+from tinyserve_llm_b200.parts.model import DecoderModel, declared_tensors
 from tinyserve_llm_b200.weights.loader import load_tensors
 from tinyserve_llm_b200.weights.random_init import random_tensors
 
@@ -46,16 +46,19 @@ def load_model(model_dir: str, dtype: str | torch.dtype = "bfloat16", device: st
                random_weights_seed: int | None = None) -> DecoderModel:
     """
     The model of the folder, chosen by its config.json.  With `random_weights_seed` the folder needs
-    only config.json: every declared tensor is drawn on the device instead of read.
+    only config.json: every declared tensor is drawn instead of read, with the generator and in the
+    dtype `write_random_model` uses, so that one seed gives one model whichever way it is made (the
+    draws run on the host, about ten seconds per billion weights, and go to the device tensor by tensor).
     """
     device = require_cuda(device)
     dtype = resolve_dtype(dtype)
     _, spec = load_model_spec(model_dir)
     declared = declared_tensors(spec)
     if random_weights_seed is None:
-        tensors = load_tensors(model_dir, declared, optional=optional_tensors(spec), device=device)
+        tensors = load_tensors(model_dir, declared, optional=spec.optional_tensors,
+                               ignored_suffixes=spec.ignored_suffixes, device=device)
     else:
-        tensors = dict(random_tensors(declared, random_weights_seed, dtype=torch.bfloat16, device=device))
+        tensors = {name: t.to(device) for name, t in random_tensors(declared, random_weights_seed, dtype=torch.bfloat16)}
     with torch.cuda.device(device):
         return DecoderModel(spec, tensors, Runtime(dtype=dtype, device=device, ops=get_ops()))
 

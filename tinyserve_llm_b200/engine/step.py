@@ -102,14 +102,17 @@ class StepRunner:
     and of the pages the step's longest request holds (both powers of two): the attention's grid
     covers what the block tables can hold, so a graph sized for the longest context the engine allows
     would make every step pay for it (64 requests of 512 tokens: 1.26 ms a step with tables for 4,096
-    tokens, 3.4 ms with tables for 131,072).  The logits such a step returns live in the graph's static
-    buffer and are overwritten by the next decode step of the same bucket: consume them (sample, copy)
-    before stepping again.  At most `max_graphs` graphs are kept; the least recently used one goes first.
+    tokens, 3.4 ms with tables for 131,072).  The logits such a step returns live in one static buffer
+    that all graphs write ([largest batch bucket, vocab] float32, allocated at the first capture) and are
+    overwritten by the next decode step: consume them (sample, copy) before stepping again.  At most
+    `max_graphs` graphs are kept; the least recently used one goes first.  `table_pages` (per layer
+    group) stands in for the pools' page counts where the widest block table is worked out: a runner on
+    a small throwaway pool can then capture the graphs the real pool will need.
     """
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: DeviceCacheStorage, *,
                  cuda_graphs: bool = True, max_decode_batch: int = 256, max_model_len: int | None = None,
-                 max_graphs: int = 48) -> None:
+                 max_graphs: int = 48, table_pages: Sequence[int] | None = None) -> None:
         self.model = model
         self.manager = manager
         self.storage = storage
@@ -121,8 +124,9 @@ class StepRunner:
         self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
         self.max_decode_batch = max_decode_batch
         longest = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
-        self._graph_widths = [max(1, min(pool.num_pages, -(-longest // manager.page_tokens)))
-                              for pool in manager.pools]
+        pool_pages = list(table_pages) if table_pages is not None else [pool.num_pages for pool in manager.pools]
+        self._graph_widths = [max(1, min(pages, -(-longest // manager.page_tokens))) for pages in pool_pages]
+        self._graph_logits: torch.Tensor | None = None   # [largest batch bucket, vocab] float32, shared by all graphs
         self._graphs: dict[tuple, _DecodeGraph] = {}    # (batch bucket, table widths) -> graph, least recently used first
         self.max_graphs = max_graphs
         self._graph_pool = None                          # the graphs' intermediates share one memory pool
@@ -370,8 +374,12 @@ class StepRunner:
             self.model.rt.ops.feed_tokens(ctx.token_ids, device_tokens)
         # once eagerly: libraries create their handles and workspaces outside the capture; the
         # step's keys and values are written by this run and again, identically, by the replay
+        if self._graph_logits is None:
+            self._graph_logits = torch.empty((self.bucket(self.max_decode_batch), self.model.spec.vocab_size),
+                                             dtype=torch.float32, device=self.device)
+        out = self._graph_logits[:size]
         x, residual = self.model.forward(ctx)
-        self.model.logits(x, residual, ctx.rows)
+        self.model.logits(x, residual, ctx.rows, out=out)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         ops = self.model.rt.ops
@@ -380,11 +388,11 @@ class StepRunner:
             self._graph_pool = torch.cuda.graph_pool_handle()
         with torch.cuda.graph(graph, pool=self._graph_pool):
             x, residual = self.model.forward(ctx)
-            logits = self.model.logits(x, residual, ctx.rows)
+            logits = self.model.logits(x, residual, ctx.rows, out=out)
         launches = ops.launches - before
         graph.replay()
         captured = _DecodeGraph(graph, index_buffer, logits, widths, launches)
-        while len(self._graphs) >= self.max_graphs:          # each graph holds a logits buffer of its own
+        while len(self._graphs) >= self.max_graphs:
             self._graphs.pop(next(iter(self._graphs)))
         self._graphs[(size, tuple(widths))] = captured
         return captured

@@ -97,9 +97,28 @@ def _log(msg: str) -> None:
 
 def build_library(force: bool = False, verbose: bool = True) -> str:
     """Path of an up-to-date kernel library, compiling it if needed."""
-    digest = source_hash()
+    return _build_shared(LIB_NAME, sources(), source_hash(), force, verbose)
+
+
+def build_extension(name: str, extra_sources: list[str], force: bool = False, verbose: bool = True) -> str:
+    """
+    Path of a shared library made of a part's own .cu files, compiled like the kernel library (same
+    flags, csrc/ on the include path) together with csrc/library.cu, so that the extension reports
+    errors through a `ts_last_error` of its own.
+    """
+    srcs = [os.path.abspath(p) for p in extra_sources] + [os.path.join(CSRC_DIR, "library.cu")]
+    h = hashlib.sha256()
+    h.update(source_hash().encode())          # flags and the headers an extension may include
+    for path in srcs:
+        h.update(os.path.basename(path).encode())
+        with open(path, "rb") as f:
+            h.update(f.read())
+    return _build_shared(f"libtinyserve_b200_{name}.so", srcs, h.hexdigest()[:20], force, verbose)
+
+
+def _build_shared(lib_name: str, srcs: list[str], digest: str, force: bool, verbose: bool) -> str:
     for folder in build_dirs():
-        lib, stamp = os.path.join(folder, LIB_NAME), os.path.join(folder, LIB_NAME + ".hash")
+        lib, stamp = os.path.join(folder, lib_name), os.path.join(folder, lib_name + ".hash")
         if not force and os.path.isfile(lib) and os.path.isfile(stamp):
             with open(stamp) as f:
                 if f.read().strip() == digest:
@@ -108,7 +127,6 @@ def build_library(force: bool = False, verbose: bool = True) -> str:
     if folder is None:
         raise BuildError(f"no writable folder for the kernel library among {build_dirs()}")
     nvcc = find_nvcc()
-    srcs = sources()
     obj_dir = os.path.join(folder, "obj-" + digest)
     os.makedirs(obj_dir, exist_ok=True)
     if verbose:
@@ -142,13 +160,13 @@ def build_library(force: bool = False, verbose: bool = True) -> str:
         workers = max(1, min(len(srcs), os.cpu_count() or 4, 8))
         with ThreadPoolExecutor(workers) as pool:
             objs = list(pool.map(compile_one, srcs))
-        tmp_lib = os.path.join(folder, f".{LIB_NAME}.{os.getpid()}")
+        tmp_lib = os.path.join(folder, f".{lib_name}.{os.getpid()}")
         proc = subprocess.run([nvcc, *LINK_FLAGS, "-o", tmp_lib, *objs], capture_output=True, text=True)
         if proc.returncode != 0:
             raise BuildError(f"linking the kernel library failed:\n{proc.stdout}\n{proc.stderr}")
-        lib = os.path.join(folder, LIB_NAME)
+        lib = os.path.join(folder, lib_name)
         os.replace(tmp_lib, lib)
-        with open(os.path.join(folder, LIB_NAME + ".hash"), "w") as f:
+        with open(os.path.join(folder, lib_name + ".hash"), "w") as f:
             f.write(digest)
     finally:
         stop.set()

@@ -51,13 +51,43 @@ _SIGNATURES = {
 _CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "f": ctypes.c_float}
 _RETURNS = {"int": ctypes.c_int, "long long": ctypes.c_longlong, "void": None, "const char*": ctypes.c_char_p}
 
+# Where a bounded wait inside a kernel gave up, by the code it left in the error word.
+_WAIT_CODES: dict[int, tuple[str, str]] = {
+    1: ("gemm_tcgen05", "TMA producer waiting for a free ring slot"),
+    2: ("gemm_tcgen05", "MMA issuer waiting for operands"),
+    3: ("gemm_tcgen05", "epilogue waiting for an accumulator"),
+    4: ("gemm_tcgen05", "MMA issuer waiting for a drained accumulator"),
+    11: ("attention_tcgen05", "loader waiting for a free key/value stage"),
+    12: ("attention_tcgen05", "MMA issuer waiting for the query tile"),
+    13: ("attention_tcgen05", "MMA issuer waiting for a key/value tile"),
+    14: ("attention_tcgen05", "MMA issuer waiting for the softmax's probabilities"),
+    15: ("attention_tcgen05", "softmax waiting for scores"),
+    16: ("attention_tcgen05", "epilogue waiting for the last product"),
+    17: ("attention_tcgen05", "softmax waiting for the previous product before rescaling"),
+}
 
-def c_int(v):
-    """Arguments go to the library as plain numbers (the functions carry their argument types)."""
-    return v
+
+def register_kernel(name: str, returns: str, arguments: str) -> None:
+    """
+    Declares an exported launcher that `Ops.call(name, ...)` may call: `returns` is one of "int"
+    (0 = success, the library's error text otherwise), "long long", "void", "const char*";
+    `arguments` one letter per argument (p: pointer or stream, i: int, l: long long, f: float).
+    A part that brings a kernel of its own (a .cu file beside the others, or an extension it loads
+    with `Ops.load_extension`) registers it here, from its own module; nothing in this file changes.
+    """
+    if returns not in _RETURNS or any(a not in _CTYPES for a in arguments):
+        raise ValueError(f"register_kernel({name!r}): unknown return type or argument letter")
+    _SIGNATURES[name] = (returns, arguments)
+    if _OPS is not None:
+        _OPS._bind(name)
 
 
-c_longlong = c_float = c_void_p = c_int
+def register_wait_codes(kernel: str, codes: dict[int, str]) -> None:
+    """Names the codes a kernel's bounded waits leave in the error word (see `Ops.error_word`)."""
+    for code, where in codes.items():
+        if code in _WAIT_CODES and _WAIT_CODES[code][0] != kernel:
+            raise ValueError(f"wait code {code} belongs to {_WAIT_CODES[code][0]} already")
+        _WAIT_CODES[code] = (kernel, where)
 
 
 def _ptr(t: torch.Tensor | None) -> int:
@@ -84,13 +114,10 @@ class Ops:
             self.lib = ctypes.CDLL(self.lib_path)
         except OSError as exc:
             raise KernelError(f"cannot load the CUDA kernel library {self.lib_path}: {exc}") from None
-        for name, (returns, arguments) in _SIGNATURES.items():
-            try:
-                fn = getattr(self.lib, name)
-            except AttributeError:
-                raise KernelError(f"the CUDA kernel library {self.lib_path} does not export {name}") from None
-            fn.restype = _RETURNS[returns]
-            fn.argtypes = [_CTYPES[a] for a in arguments]
+        self._functions: dict[str, object] = {}       # launcher name -> (ctypes function, library it came from)
+        self._extensions: dict[str, ctypes.CDLL] = {}
+        for name in _SIGNATURES:
+            self._bind(name)
         self.launches = 0            # kernels of this library launched (or captured into a graph) so far
         self.calls: dict[str, int] = {}   # calls per exported launcher (and "library_mm": products left to cuBLAS)
         self._error_word: torch.Tensor | None = None
@@ -106,14 +133,79 @@ class Ops:
 
     def set_chaining(self, enabled: bool) -> None:
         self.chaining = bool(enabled)
-        self.lib.ts_set_chaining(c_int(1 if enabled else 0))
+        self.lib.ts_set_chaining(1 if enabled else 0)
 
     # ------------------------------------------------------------------ helpers
+    def _bind(self, name: str, lib: ctypes.CDLL | None = None) -> None:
+        returns, arguments = _SIGNATURES[name]
+        owner = None
+        for candidate in ([lib] if lib is not None else [self.lib, *self._extensions.values()]):
+            if hasattr(candidate, name):
+                owner = candidate
+                break
+        if owner is None:
+            raise KernelError(f"the CUDA kernel library {self.lib_path} does not export {name}")
+        fn = getattr(owner, name)
+        fn.restype = _RETURNS[returns]
+        fn.argtypes = [_CTYPES[a] for a in arguments]
+        self._functions[name] = (fn, owner)
+
     def _call(self, name: str, *args) -> None:
-        if getattr(self.lib, name)(*args) != 0:
-            raise KernelError(self.lib.ts_last_error().decode())
+        fn, owner = self._functions[name]
+        if fn(*args) != 0:
+            raise KernelError(owner.ts_last_error().decode())
         self.launches += 1
         self.calls[name] = self.calls.get(name, 0) + 1
+
+    def call(self, name: str, *args):
+        """
+        Calls a registered launcher (`register_kernel`) with plain numbers and `data_ptr()`s.  An
+        "int" launcher is a kernel launch: nonzero raises KernelError with the library's text, and
+        the launch is counted.  Other return types hand back their value.
+        """
+        if name not in self._functions:
+            if name not in _SIGNATURES:
+                raise KernelError(f"{name} is not a registered kernel launcher; call register_kernel first")
+            self._bind(name)
+        if _SIGNATURES[name][0] == "int":
+            return self._call(name, *args)
+        return self._functions[name][0](*args)
+
+    @staticmethod
+    def stream() -> int:
+        """The current CUDA stream's handle, as launchers take it."""
+        return _stream()
+
+    def error_word(self) -> torch.Tensor:
+        """
+        One int32 in pinned host memory that kernels with bounded waits write a code into when a
+        wait runs out (its `data_ptr()` is what their launchers take).  `check_device_errors` reads
+        it before every step and names the kernel by the registered code (`register_wait_codes`).
+        """
+        if self._error_word is None:
+            self._error_word = torch.zeros((1,), dtype=torch.int32).pin_memory()
+        return self._error_word
+
+    def load_extension(self, name: str, sources: list[str], kernels: dict[str, tuple[str, str]]) -> None:
+        """
+        Compiles a part's own .cu files for sm_100a into a shared library of their own (they may
+        include this library's common.cuh and report errors the same way), loads it and registers
+        its launchers: `kernels` maps an exported name to (returns, arguments) as `register_kernel`
+        takes them.  Done once per name and process.
+        """
+        if name in self._extensions:
+            return
+        from tinyserve_llm_b200.ops.build import build_extension
+        path = build_extension(name, sources)
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as exc:
+            raise KernelError(f"cannot load the kernel extension {path}: {exc}") from None
+        lib.ts_last_error.restype = ctypes.c_char_p
+        self._extensions[name] = lib
+        for kernel, (returns, arguments) in kernels.items():
+            register_kernel(kernel, returns, arguments)
+            self._bind(kernel, lib)
 
     @staticmethod
     def _check(t: torch.Tensor, name: str, dtype: torch.dtype | tuple | None = None, dims: int | None = None) -> None:
@@ -133,15 +225,15 @@ class Ops:
         self._check(table, "embedding table", tuple(_DTYPE_CODE), 2)
         self._check(ids, "token ids", torch.int32, 1)
         out = torch.empty((ids.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
-        self._call("ts_embedding", _ptr(table), _ptr(ids), _ptr(out), c_int(ids.shape[0]), c_int(table.shape[1]),
-                   c_int(table.shape[0]), c_int(_DTYPE_CODE[table.dtype]), _stream())
+        self._call("ts_embedding", _ptr(table), _ptr(ids), _ptr(out), ids.shape[0], table.shape[1],
+                   table.shape[0], _DTYPE_CODE[table.dtype], _stream())
         return out
 
     def feed_tokens(self, ids: torch.Tensor, source: torch.Tensor) -> None:
         """In place: an id slot that holds -(j + 2) becomes source[j] (the previous step's sample j, still on the device)."""
         self._check(ids, "token ids", torch.int32, 1)
         self._check(source, "sampled tokens", torch.int32, 1)
-        self._call("ts_feed_tokens", _ptr(ids), c_int(ids.shape[0]), _ptr(source), c_int(source.shape[0]), _stream())
+        self._call("ts_feed_tokens", _ptr(ids), ids.shape[0], _ptr(source), source.shape[0], _stream())
 
     def add_rmsnorm(self, x: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, eps: float,
                     rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
@@ -172,8 +264,8 @@ class Ops:
             out = torch.empty((count, hidden), dtype=x.dtype, device=x.device)
             new_residual, residual_out = residual, None
         self._call("ts_add_rmsnorm", _ptr(x), _ptr(residual), _ptr(weight), _ptr(out), _ptr(residual_out), _ptr(rows),
-                   c_int(count), c_int(hidden), c_float(eps), c_int(_DTYPE_CODE[x.dtype]),
-                   c_int(_DTYPE_CODE[weight.dtype]), _stream())
+                   count, hidden, eps, _DTYPE_CODE[x.dtype],
+                   _DTYPE_CODE[weight.dtype], _stream())
         return out, new_residual
 
     def rope_store(self, qkv: torch.Tensor, ctx, binding, table: torch.Tensor | None, nh: int, nkv: int, hd: int) -> None:
@@ -186,11 +278,11 @@ class Ops:
         if table is not None:
             self._check(table, "rotary table", torch.float32, 2)
             rows, rot = table.shape
-        self._call("ts_rope_store", _ptr(qkv), _ptr(ctx.positions), _ptr(ctx.seq_of_token), _ptr(table), c_int(rows),
-                   c_int(rot), _ptr(binding.block_table), c_int(binding.table_width), _ptr(binding.k_pool),
-                   _ptr(binding.v_pool), c_longlong(binding.page_stride), c_longlong(binding.entry_offset),
-                   c_int(binding.page_tokens), c_int(binding.num_pages), c_int(qkv.shape[0]), c_int(nh), c_int(nkv),
-                   c_int(hd), c_int(1 if binding.writes else 0), c_int(_DTYPE_CODE[qkv.dtype]), _stream())
+        self._call("ts_rope_store", _ptr(qkv), _ptr(ctx.positions), _ptr(ctx.seq_of_token), _ptr(table), rows,
+                   rot, _ptr(binding.block_table), binding.table_width, _ptr(binding.k_pool),
+                   _ptr(binding.v_pool), binding.page_stride, binding.entry_offset,
+                   binding.page_tokens, binding.num_pages, qkv.shape[0], nh, nkv,
+                   hd, 1 if binding.writes else 0, _DTYPE_CODE[qkv.dtype], _stream())
 
     def linear_rope_store(self, x: torch.Tensor, weight: torch.Tensor, ctx, binding, table: torch.Tensor | None,
                           nh: int, nkv: int, hd: int) -> torch.Tensor | None:
@@ -212,12 +304,12 @@ class Ops:
             self._check(table, "rotary table", torch.float32, 2)
             rows = table.shape[0]
         qkv = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.bfloat16, device=x.device)
-        self._call("ts_skinny_qkv_rope_store", _ptr(weight), _ptr(x), _ptr(qkv), c_int(x.shape[0]), c_int(x.shape[1]),
-                   c_longlong(x.stride(0)), _ptr(ctx.positions), _ptr(ctx.seq_of_token), _ptr(table), c_int(rows),
-                   c_int(hd), _ptr(binding.block_table), c_int(binding.table_width), _ptr(binding.k_pool),
-                   _ptr(binding.v_pool), c_longlong(binding.page_stride), c_longlong(binding.entry_offset),
-                   c_int(binding.page_tokens), c_int(binding.num_pages), c_int(nh), c_int(nkv), c_int(hd),
-                   c_int(1 if binding.writes else 0), _stream())
+        self._call("ts_skinny_qkv_rope_store", _ptr(weight), _ptr(x), _ptr(qkv), x.shape[0], x.shape[1],
+                   x.stride(0), _ptr(ctx.positions), _ptr(ctx.seq_of_token), _ptr(table), rows,
+                   hd, _ptr(binding.block_table), binding.table_width, _ptr(binding.k_pool),
+                   _ptr(binding.v_pool), binding.page_stride, binding.entry_offset,
+                   binding.page_tokens, binding.num_pages, nh, nkv, hd,
+                   1 if binding.writes else 0, _stream())
         return qkv
 
     def paged_attention(self, qkv: torch.Tensor, ctx, binding, nh: int, nkv: int, hd: int, scale: float,
@@ -230,49 +322,47 @@ class Ops:
         self._check(qkv, "qkv", tuple(_DTYPE_CODE), 2)
         out = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
         if (not generic and qkv.dtype == torch.bfloat16 and getattr(ctx, "cu_q", None) is not None
-                and self.lib.ts_attention_bf16_supported(c_int(hd), c_int(binding.page_tokens), c_int(nh), c_int(nkv))):
+                and self.lib.ts_attention_bf16_supported(hd, binding.page_tokens, nh, nkv)):
             num_seqs = ctx.ctx_lens.shape[0]
             scratch, floats = None, 0
             max_q_len = ctx.max_q_len
             prefill_seqs = getattr(ctx, "prefill_seqs", None)      # the step runner lists them; a bare context may not
             num_prefill = prefill_seqs.shape[0] if prefill_seqs is not None else 0
             if (max_q_len > 1 and self.tcgen05_attention and self.lib.ts_attention_tcgen05_supported(
-                    c_int(hd), c_int(binding.page_tokens), c_int(nh), c_int(nkv), c_int(window))):
+                    hd, binding.page_tokens, nh, nkv, window)):
                 # prompt portions on the tcgen05 kernel; requests that feed one token stay with the split-key kernels
                 per_entry = nkv * binding.page_tokens * hd
-                if self._error_word is None:
-                    self._error_word = torch.zeros((1,), dtype=torch.int32).pin_memory()
                 self._call("ts_prefill_attention_tcgen05", _ptr(qkv), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
-                           c_int(binding.num_pages), c_int(binding.page_stride // per_entry),
-                           c_int(binding.entry_offset // per_entry), c_int(binding.page_tokens), _ptr(binding.block_table),
-                           c_int(binding.table_width), _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), c_int(num_seqs),
-                           c_int(qkv.shape[0]), c_int(max_q_len), c_int(nh), c_int(nkv), c_int(hd), c_float(scale),
-                           _ptr(prefill_seqs), c_int(num_prefill), c_void_p(self._error_word.data_ptr()), _stream())
+                           binding.num_pages, binding.page_stride // per_entry,
+                           binding.entry_offset // per_entry, binding.page_tokens, _ptr(binding.block_table),
+                           binding.table_width, _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), num_seqs,
+                           qkv.shape[0], max_q_len, nh, nkv, hd, scale,
+                           _ptr(prefill_seqs), num_prefill, self.error_word().data_ptr(), _stream())
                 if ctx.min_q_len > 1:
                     return out
                 max_q_len = 1
             if ctx.min_q_len <= 1:
-                floats = self.lib.ts_attention_bf16_scratch_floats(c_int(num_seqs), c_int(nh), c_int(hd),
-                                                                   c_int(ctx.max_ctx_len))
+                floats = self.lib.ts_attention_bf16_scratch_floats(num_seqs, nh, hd,
+                                                                   ctx.max_ctx_len)
                 key = ("attention", floats)
                 scratch = ctx.scratch.get(key)
                 if scratch is None:
                     scratch = ctx.scratch[key] = torch.empty((floats,), dtype=torch.float32, device=qkv.device)
             self._call("ts_paged_attention_bf16", _ptr(qkv), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
-                       c_longlong(binding.page_stride), c_longlong(binding.entry_offset), c_int(binding.page_tokens),
-                       c_int(binding.num_pages), _ptr(binding.block_table), c_int(binding.table_width),
-                       _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), c_int(num_seqs), c_int(max_q_len),
-                       c_int(min(ctx.min_q_len, max_q_len)), c_int(ctx.max_ctx_len), c_int(nh), c_int(nkv), c_int(hd),
-                       c_float(scale), c_int(window), _ptr(scratch), c_longlong(floats), _ptr(prefill_seqs),
-                       c_int(num_prefill), _stream())
+                       binding.page_stride, binding.entry_offset, binding.page_tokens,
+                       binding.num_pages, _ptr(binding.block_table), binding.table_width,
+                       _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), num_seqs, max_q_len,
+                       min(ctx.min_q_len, max_q_len), ctx.max_ctx_len, nh, nkv, hd,
+                       scale, window, _ptr(scratch), floats, _ptr(prefill_seqs),
+                       num_prefill, _stream())
             if ctx.min_q_len <= 1:
                 self.launches += 1 if max_q_len <= 1 else 2          # decode + combine (+ prefill) in one call
             return out
         self._call("ts_paged_attention_generic", _ptr(qkv), _ptr(out), _ptr(binding.k_pool), _ptr(binding.v_pool),
-                   c_longlong(binding.page_stride), c_longlong(binding.entry_offset), c_int(binding.page_tokens),
-                   c_int(binding.num_pages), _ptr(binding.block_table), c_int(binding.table_width),
-                   _ptr(ctx.positions), _ptr(ctx.seq_of_token), c_int(qkv.shape[0]), c_int(nh), c_int(nkv), c_int(hd),
-                   c_float(scale), c_int(window), c_int(_DTYPE_CODE[qkv.dtype]), _stream())
+                   binding.page_stride, binding.entry_offset, binding.page_tokens,
+                   binding.num_pages, _ptr(binding.block_table), binding.table_width,
+                   _ptr(ctx.positions), _ptr(ctx.seq_of_token), qkv.shape[0], nh, nkv, hd,
+                   scale, window, _DTYPE_CODE[qkv.dtype], _stream())
         return out
 
     def silu_mul(self, gate_up: torch.Tensor) -> torch.Tensor:
@@ -281,38 +371,46 @@ class Ops:
             raise KernelError("gate_up rows must hold gate and up halves of equal width")
         inter = gate_up.shape[1] // 2
         out = torch.empty((gate_up.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
-        self._call("ts_silu_mul", _ptr(gate_up), _ptr(out), c_int(gate_up.shape[0]), c_int(inter),
-                   c_int(_DTYPE_CODE[gate_up.dtype]), _stream())
+        self._call("ts_silu_mul", _ptr(gate_up), _ptr(out), gate_up.shape[0], inter,
+                   _DTYPE_CODE[gate_up.dtype], _stream())
         return out
 
-    def linear(self, x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    def linear(self, x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
+               out: torch.Tensor | None = None) -> torch.Tensor:
         """
         x [M, K] . weight[N, K]^T.  float32: the engine's FFMA kernel.  bfloat16: up to 32 rows of x on
         the engine's weight-streaming kernel, more on the library product (cuBLAS through torch.mm).
+        `out` (contiguous [M, N] of the output dtype) receives the product instead of a new tensor.
         """
         self._check(x, "x", tuple(_DTYPE_CODE), 2)
         self._check(weight, "weight", x.dtype, 2)
         if x.shape[1] != weight.shape[1]:
             raise KernelError(f"linear: x has {x.shape[1]} columns, the weight {weight.shape[1]}")
-        if x.dtype == torch.float32:
-            out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
-            self._call("ts_sgemm_nt", _ptr(x), _ptr(weight), _ptr(out), c_int(x.shape[0]), c_int(weight.shape[0]),
-                       c_int(x.shape[1]), c_longlong(x.shape[1]), c_longlong(weight.shape[1]),
-                       c_longlong(weight.shape[0]), _stream())
-            return out
         out_dtype = out_dtype or x.dtype
-        if self._skinny(x, weight):
+        if x.dtype == torch.float32 and out_dtype != torch.float32:
+            raise KernelError("linear: the float32 product has float32 output")
+        if out is None:
             out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
-            self._call("ts_skinny_linear", _ptr(weight), _ptr(x), _ptr(out), c_int(x.shape[0]), c_int(weight.shape[0]),
-                       c_int(x.shape[1]), c_longlong(x.shape[1]), c_longlong(weight.shape[0]), c_int(0),
-                       c_int(_DTYPE_CODE[out_dtype]), _stream())
+        else:
+            self._check(out, "out", out_dtype, 2)
+            if tuple(out.shape) != (x.shape[0], weight.shape[0]):
+                raise KernelError(f"linear: out is {tuple(out.shape)}, the product {(x.shape[0], weight.shape[0])}")
+        if x.dtype == torch.float32:
+            self._call("ts_sgemm_nt", _ptr(x), _ptr(weight), _ptr(out), x.shape[0], weight.shape[0],
+                       x.shape[1], x.shape[1], weight.shape[1],
+                       weight.shape[0], _stream())
+            return out
+        if self._skinny(x, weight):
+            self._call("ts_skinny_linear", _ptr(weight), _ptr(x), _ptr(out), x.shape[0], weight.shape[0],
+                       x.shape[1], x.shape[1], weight.shape[0], 0,
+                       _DTYPE_CODE[out_dtype], _stream())
             if out_dtype == torch.float32:
                 self.calls["ts_skinny_linear:float32_out"] = self.calls.get("ts_skinny_linear:float32_out", 0) + 1
             return out
         self.calls["library_mm"] = self.calls.get("library_mm", 0) + 1
         if out_dtype != x.dtype:
-            return torch.mm(x, weight.t(), out_dtype=out_dtype)
-        return torch.mm(x, weight.t())
+            return torch.mm(x, weight.t(), out_dtype=out_dtype, out=out)
+        return torch.mm(x, weight.t(), out=out)
 
     def gemm_tcgen05(self, x: torch.Tensor, weight: torch.Tensor, *, swiglu: bool = False,
                      out_dtype: torch.dtype | None = None) -> torch.Tensor:
@@ -331,11 +429,9 @@ class Ops:
         out = torch.empty((M, cols), dtype=out_dtype, device=x.device)
         if M == 0:
             return out
-        if self._error_word is None:
-            self._error_word = torch.zeros((1,), dtype=torch.int32).pin_memory()    # device-visible host memory
-        self._call("ts_gemm_tcgen05", _ptr(weight), _ptr(x), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(K),
-                   c_longlong(cols), c_int(1 if swiglu else 0), c_int(_DTYPE_CODE[out_dtype]),
-                   c_void_p(self._error_word.data_ptr()), _stream())
+        self._call("ts_gemm_tcgen05", _ptr(weight), _ptr(x), _ptr(out), M, N, K, K,
+                   cols, 1 if swiglu else 0, _DTYPE_CODE[out_dtype],
+                   self.error_word().data_ptr(), _stream())
         return out
 
     def check_device_errors(self) -> None:
@@ -343,8 +439,8 @@ class Ops:
         if self._error_word is not None and int(self._error_word[0]) != 0:
             code = int(self._error_word[0])
             self._error_word[0] = 0
-            where = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, "unknown")
-            raise KernelError(f"gemm_tcgen05: a {where} wait on an mbarrier ran out of time (code {code})")
+            kernel, where = _WAIT_CODES.get(code, ("a kernel", "an unregistered wait"))
+            raise KernelError(f"{kernel}: a bounded wait ran out of time ({where}; code {code})")
 
     def _skinny(self, x: torch.Tensor, weight: torch.Tensor) -> bool:
         """A few rows of bfloat16 x (a decode step): the engine's own weight-streaming kernel takes them."""
@@ -362,16 +458,16 @@ class Ops:
         # kernel is faster (18 against 15 us at 16 rows of Llama 3.2 1B's sizes on a B200)
         if not (self._skinny(x, gate_up_weight) and x.shape[0] <= 8):
             if x.dtype == torch.bfloat16 and x.shape[0] >= self.tcgen05_swiglu_min_rows and self.lib.ts_gemm_tcgen05_supported(
-                    _ptr(gate_up_weight), _ptr(x), c_int(x.shape[0]), c_int(gate_up_weight.shape[0]), c_int(x.shape[1]),
-                    c_longlong(x.shape[1])):
+                    _ptr(gate_up_weight), _ptr(x), x.shape[0], gate_up_weight.shape[0], x.shape[1],
+                    x.shape[1]):
                 # tcgen05 product with the activation in its epilogue: the [M, 2I] product never reaches memory
                 return self.gemm_tcgen05(x, gate_up_weight, swiglu=True)
             return self.silu_mul(self.linear(x, gate_up_weight))
         inter = gate_up_weight.shape[0] // 2
         out = torch.empty((x.shape[0], inter), dtype=x.dtype, device=x.device)
-        self._call("ts_skinny_linear", _ptr(gate_up_weight), _ptr(x), _ptr(out), c_int(x.shape[0]),
-                   c_int(gate_up_weight.shape[0]), c_int(x.shape[1]), c_longlong(x.shape[1]), c_longlong(inter),
-                   c_int(1), c_int(_DTYPE_CODE[x.dtype]), _stream())
+        self._call("ts_skinny_linear", _ptr(gate_up_weight), _ptr(x), _ptr(out), x.shape[0],
+                   gate_up_weight.shape[0], x.shape[1], x.shape[1], inter,
+                   1, _DTYPE_CODE[x.dtype], _stream())
         return out
 
     def sample(self, logits: torch.Tensor, temperatures: torch.Tensor, keys: torch.Tensor) -> torch.Tensor:
@@ -383,10 +479,10 @@ class Ops:
         if temperatures.shape[0] != rows or tuple(keys.shape) != (rows, 2):
             raise KernelError("sample: one temperature and one key pair per logits row are needed")
         out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
-        words = int(self.lib.ts_sample_scratch_words(c_int(rows), c_int(logits.shape[1])))
+        words = int(self.lib.ts_sample_scratch_words(rows, logits.shape[1]))
         scratch = torch.empty((max(words, 1),), dtype=torch.int32, device=logits.device)    # the chunks' best (value, index)
-        self._call("ts_sample", _ptr(logits), c_longlong(logits.shape[1]), _ptr(temperatures), _ptr(keys), _ptr(out),
-                   c_int(rows), c_int(logits.shape[1]), _ptr(scratch), c_int(words), _stream())
+        self._call("ts_sample", _ptr(logits), logits.shape[1], _ptr(temperatures), _ptr(keys), _ptr(out),
+                   rows, logits.shape[1], _ptr(scratch), words, _stream())
         self.launches += 1                                   # two kernels in one call
         return out
 
@@ -394,9 +490,9 @@ class Ops:
         """Pools are [pages, entries, kv_heads, page_tokens, head_dim]."""
         self._check(k_pool, "k_pool", tuple(_DTYPE_CODE), 5)
         pages, entries, nkv, page_tokens, hd = k_pool.shape
-        self._call("ts_copy_page_slots", _ptr(k_pool), _ptr(v_pool), c_int(pages), c_int(entries), c_int(nkv),
-                   c_int(page_tokens), c_int(hd), c_int(k_pool.dtype.itemsize), c_int(src), c_int(dst),
-                   c_int(num_slots), _stream())
+        self._call("ts_copy_page_slots", _ptr(k_pool), _ptr(v_pool), pages, entries, nkv,
+                   page_tokens, hd, k_pool.dtype.itemsize, src, dst,
+                   num_slots, _stream())
 
 
 _OPS: Ops | None = None

@@ -17,12 +17,25 @@ from tinyserve_llm_b200.parts.base import KVNeed, Mixer, Runtime, TensorDecl, pa
 from tinyserve_llm_b200.parts.linear import Linear, fuse_rows
 
 
+MAX_HEAD_DIM = 256      # csrc/attention_generic.cu, the kernel every size falls back to
+
+
 @register_part("mixer", "attention")
 class PagedAttention(Mixer):
     graph_safe = True
 
     @classmethod
+    def validate(cls, spec: AttentionSpec) -> None:
+        """Sizes no attention kernel takes are refused when the model is described or built, not at its first step."""
+        if spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"num_heads={spec.num_heads} is not a multiple of num_kv_heads={spec.num_kv_heads}")
+        if spec.head_dim <= 0 or spec.head_dim % 16 or spec.head_dim > MAX_HEAD_DIM:
+            raise ValueError(f"head_dim={spec.head_dim} is not supported: the attention kernels take multiples of 16 "
+                             f"up to {MAX_HEAD_DIM}")
+
+    @classmethod
     def declare(cls, spec: AttentionSpec) -> dict[str, TensorDecl]:
+        cls.validate(spec)
         q = spec.num_heads * spec.head_dim
         kv = spec.num_kv_heads * spec.head_dim
         return {
@@ -34,8 +47,7 @@ class PagedAttention(Mixer):
 
     def __init__(self, spec: AttentionSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         super().__init__(spec, tensors, rt)
-        if spec.num_heads % spec.num_kv_heads:
-            raise ValueError(f"num_heads={spec.num_heads} is not a multiple of num_kv_heads={spec.num_kv_heads}")
+        self.validate(spec)
         self.qkv = Linear(fuse_rows([tensors["q_proj.weight"], tensors["k_proj.weight"],
                                      tensors["v_proj.weight"]]), rt)
         self.out = Linear(tensors["o_proj.weight"], rt)

@@ -26,5 +26,6 @@ class Linear:
         self.weight = weight.to(device=rt.device, dtype=rt.dtype).contiguous()
         self.out_features, self.in_features = self.weight.shape
 
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-        return self.rt.ops.linear(x, self.weight, out_dtype=out_dtype)
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None,
+                 out: torch.Tensor | None = None) -> torch.Tensor:
+        return self.rt.ops.linear(x, self.weight, out_dtype=out_dtype, out=out)

@@ -31,11 +31,6 @@ def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
     return out
 
 
-def optional_tensors(spec: ModelSpec) -> list[str]:
-    """Names a checkpoint may carry without the model using them (a tied model's lm_head copy)."""
-    return ["lm_head.weight"] if spec.lm_head_name is None else []
-
-
 class DecoderModel:
     def __init__(self, spec: ModelSpec, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         self.spec = spec
@@ -94,7 +89,8 @@ class DecoderModel:
             x, residual = self.blocks[entry.block].forward(x, residual, ctx, ctx.binding(entry))
         return x, residual
 
-    def logits(self, x: torch.Tensor, residual: torch.Tensor | None, rows: torch.Tensor) -> torch.Tensor:
-        """float32 [len(rows), vocab]: final norm and vocabulary projection of the wanted rows only."""
+    def logits(self, x: torch.Tensor, residual: torch.Tensor | None, rows: torch.Tensor,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+        """float32 [len(rows), vocab] (into `out` if given): final norm and vocabulary projection of the wanted rows only."""
         h, _ = self.final_norm.forward(x, residual, rows)
-        return self.lm_head(h, out_dtype=torch.float32)
+        return self.lm_head(h, out_dtype=torch.float32, out=out)

@@ -3,7 +3,7 @@ Load a model folder's tensors by name and check them against what the model's pa
 
 Reference behaviour (model/loader.py:28-70): every model*.safetensors of the folder is read,
 `rotary_emb.inv_freq` buffers are skipped, a tied checkpoint's `lm_head.weight` is skipped, and an
-unfilled parameter raises.  Here every problem of the checkpoint (missing tensors, unexpected
+unfilled parameter raises.  Which names may be skipped comes with the model description, not from here.  Here every problem of the checkpoint (missing tensors, unexpected
 tensors, wrong shapes) is gathered into one error.
 
 Stored dtypes are kept: bfloat16 stays bfloat16, a tensor stored in 32-bit floats stays so, integer
@@ -20,9 +20,6 @@ import torch
 
 from tinyserve_llm_b200.parts.base import TensorDecl
 from tinyserve_llm_b200.weights.safetensors_io import SafetensorsError, SafetensorsFile
-
-IGNORED_SUFFIXES = ("rotary_emb.inv_freq",)
-
 
 class CheckpointError(ValueError):
     """The checkpoint does not fit the model: lists missing, unexpected and misshapen tensors."""
@@ -64,14 +61,16 @@ def _kept_dtype(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
-def load_tensors(model_dir: str, declared: Mapping[str, TensorDecl], *,
-                 optional: Iterable[str] = (), device: torch.device | str = "cpu") -> dict[str, torch.Tensor]:
+def load_tensors(model_dir: str, declared: Mapping[str, TensorDecl], *, optional: Iterable[str] = (),
+                 ignored_suffixes: Iterable[str] = (), device: torch.device | str = "cpu") -> dict[str, torch.Tensor]:
     """
-    {name: tensor on `device`} for every declared name.  `optional` names are accepted and dropped
-    when present (a tied checkpoint's lm_head.weight).  Raises CheckpointError listing everything
-    that is wrong at once.
+    {name: tensor on `device`} for every declared name.  `optional` names and names ending in one
+    of `ignored_suffixes` are accepted and dropped when present; which they are is the model
+    description's business (`ModelSpec.optional_tensors`, `ModelSpec.ignored_suffixes`).  Raises
+    CheckpointError listing everything that is wrong at once.
     """
     optional = set(optional)
+    ignored = tuple(ignored_suffixes)
     files = [SafetensorsFile(p) for p in checkpoint_files(model_dir)]
     try:
         where: dict[str, SafetensorsFile] = {}
@@ -79,7 +78,7 @@ def load_tensors(model_dir: str, declared: Mapping[str, TensorDecl], *,
         wrong_shape: list[tuple[str, tuple[int, ...], tuple[int, ...]]] = []
         for f in files:
             for name, entry in f.entries.items():
-                if name.endswith(IGNORED_SUFFIXES) or name in optional:
+                if (ignored and name.endswith(ignored)) or name in optional:
                     continue
                 if name not in declared:
                     unexpected.append(name)
@@ -102,4 +101,4 @@ def load_tensors(model_dir: str, declared: Mapping[str, TensorDecl], *,
             f.close()
 
 
-__all__ = ["CheckpointError", "SafetensorsError", "checkpoint_files", "load_tensors", "IGNORED_SUFFIXES"]
+__all__ = ["CheckpointError", "SafetensorsError", "checkpoint_files", "load_tensors"]
