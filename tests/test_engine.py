@@ -295,7 +295,7 @@ def test_decode_graphs_follow_the_longest_request(model_folders, dtype):
                 manager.commit(i, 1)
         outs[graphs] = got
         if graphs:
-            widths = {key[1][0] for key in runner._graphs}
+            widths = {shape.widths[0] for shape in runner._graphs}
             assert widths == expected and len(widths) >= 5, (widths, expected)    # 2 pages at first, 8 at the end
             assert runner.graph_replays == steps
     for a, b in zip(outs[True], outs[False]):
@@ -312,6 +312,64 @@ def test_decode_graphs_follow_the_longest_request(model_folders, dtype):
         manager.commit(0, 1)
         assert len(runner._graphs) <= 2
     assert runner.graph_replays == steps
+
+
+@pytest.mark.parametrize("name, dtype, page", [("b", "float32", PAGE_B), ("d", "bfloat16", 64), ("d", "float32", 64)])
+def test_steps_with_prompt_portions_are_replayed_from_graphs(model_folders, name, dtype, page):
+    """
+    Three requests decode while two more arrive in portions of 40 and 24 tokens (the last portions are
+    shorter): from the second time a shape of step is met it is captured and replayed, padded to its
+    buckets.  float32 gives bit for bit what steps launched kernel by kernel give; bfloat16 the same
+    up to the library product's choice of kernel for another number of rows.
+    """
+    from tinyserve_llm_b200.engine.loading import build_cache, load_model
+    from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
+    raw = {"b": TINY_B, "d": TINY_D}[name]
+    vocab = raw["vocab_size"]
+    model = load_model(model_folders[name], dtype, "cuda")
+    decoding = [ru.random_ids(vocab, n, 700 + n) for n in (page + 3, 9, 2 * page)]
+    arriving = {"x": ru.random_ids(vocab, 190, 801), "y": ru.random_ids(vocab, 100, 802)}
+    outs = {}
+    for graphs in (True, False):
+        _, manager, storage = build_cache(model, page, 40, caching=False)
+        runner = StepRunner(model, manager, storage, cuda_graphs=graphs)
+        for i, p in enumerate(decoding):
+            assert manager.admit(i, p)
+        runner.step([StepEntry(i, p, []) for i, p in enumerate(decoding)])
+        for i, p in enumerate(decoding):
+            manager.commit(i, len(p))
+        fed = {"x": 0, "y": 0}
+        got = []
+        for t in range(9):
+            entries = []
+            for i in range(3):
+                manager.extend(i, [(11 * t + i) % vocab])
+                entries.append(StepEntry(i, [(11 * t + i) % vocab], [0]))
+            for key, size in (("x", 40), ("y", 24)):
+                tokens = arriving[key][fed[key]:fed[key] + size]
+                if not tokens:
+                    continue
+                if fed[key] == 0:
+                    assert manager.admit(key, tokens)
+                else:
+                    manager.extend(key, tokens)
+                last = fed[key] + len(tokens) == len(arriving[key])
+                entries.append(StepEntry(key, tokens, [len(tokens) - 1] if last else []))
+                fed[key] += len(tokens)
+            got.append(runner.step(entries).cpu().clone())
+            for e in entries:
+                manager.commit(e.seq_id, len(e.tokens))
+        outs[graphs] = got
+        if graphs:
+            shapes = [s for s in runner._graphs if s.portions]
+            assert shapes and runner.graph_replays >= 3, (runner.graph_replays, list(runner._graphs))
+            assert all(s.tokens % 64 == 0 and s.seqs == 8 for s in shapes)
+    for a, b in zip(outs[True], outs[False]):
+        assert a.shape == b.shape
+        if dtype == "float32":
+            assert torch.equal(a, b)
+        else:
+            torch.testing.assert_close(a, b, atol=0.012 * float(b.abs().max()), rtol=0.0)
 
 
 def test_multi_turn_replay_reuses_histories_and_changes_no_token(model_folders, tmp_path):

@@ -220,7 +220,7 @@ struct AttnParams {
     int num_seqs, nh, nkv;
     float scale_log2;
     int window;
-    const int* prefill_seqs;   // requests that feed more than one token, for the prefill grid; null: every request
+    const int* prefill_seqs;   // requests that feed more than one token, for the prefill grid (-1: none); null: every request
     // decode only
     float* partial_o;      // [seq][head][split][HD]
     float* partial_ml;     // [seq][head][split][2]
@@ -248,6 +248,7 @@ __global__ void __launch_bounds__(128) prefill_attention_kernel(AttnParams p) {
     __nv_bfloat16* q_tile = reinterpret_cast<__nv_bfloat16*>(smem_raw);             // [64][HD]
     __nv_bfloat16* kv_tiles = q_tile + TILE * HD;                                     // 2 stages x (K, V) x [64][HD]
     const int seq = p.prefill_seqs ? p.prefill_seqs[blockIdx.z] : (int)blockIdx.z, head = blockIdx.y;
+    if (seq < 0) return;                                                              // a padding entry of the list (a step replayed from a graph)
     const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
     if (q_len <= 1) return;                                                           // decode rows go to the other kernel
     const int tiles = (q_len + TILE - 1) / TILE;

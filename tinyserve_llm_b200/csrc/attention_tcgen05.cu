@@ -173,7 +173,7 @@ struct FlashParams {
     int table_width;
     const int* cu_q;
     const int* ctx_lens;
-    const int* prefill_seqs;          // requests that feed more than one token; null: every request has CTAs
+    const int* prefill_seqs;          // requests that feed more than one token (-1: none); null: every request has CTAs
     int nh, nkv;
     int page_tokens, num_pages;
     int entries, entry;               // cache entries of the layer group; this layer's index among them
@@ -201,6 +201,7 @@ __global__ void __launch_bounds__(THREADS, 2) prefill_attention_tcgen05_kernel(c
     // the short ones fill the SMs as the long ones finish.
     const int seq = p.prefill_seqs ? p.prefill_seqs[blockIdx.z] : (int)blockIdx.z, head = blockIdx.x;
     chain_wait();                                    // q, k and v of the step come from kernels ahead on the stream
+    if (seq < 0) return;                             // a padding entry of the list (a step replayed from a graph)
     const int q_begin = p.cu_q[seq], q_len = p.cu_q[seq + 1] - q_begin;
     if (q_len <= 1) return;                          // decode rows go to the split-key kernels
     const int tiles = (q_len + QROWS - 1) / QROWS;

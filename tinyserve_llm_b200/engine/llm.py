@@ -23,7 +23,7 @@ from tinyserve_llm_b200.cache.storage import DeviceCacheStorage
 from tinyserve_llm_b200.engine.loading import build_cache, load_model, require_cuda, resolve_dtype
 from tinyserve_llm_b200.engine.scheduler import RequestOutput, ScheduledSeq, Scheduler, SchedulerConfig, SchedulerStats
 from tinyserve_llm_b200.engine.sequence import SamplingParams, SequenceStatus
-from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
+from tinyserve_llm_b200.engine.step import StepEntry, StepRunner, StepShape
 from tinyserve_llm_b200.sampling.sampler import PendingTokens, Sampler
 
 logger = logging.getLogger(__name__)
@@ -145,17 +145,19 @@ class LLM:
         `utilisation` x the device's memory.  tinyserve-llm warms up with the token budget spread
         over as many sequences as the cap allows, every one sampling, so that the [rows, vocab]
         logits and the sampler's buffers are in the measured peak (engine/llm_engine.py:112-140).
-        The same step runs here, on a throwaway pool.  Then, where decode steps will be replayed
-        from CUDA graphs, the widest one the configuration allows (every sequence slot taken, block
-        tables for `max_model_len`) is captured once: what the graphs hold (their shared logits
-        buffer and their memory pool, which the widest graph sizes) stays allocated beside every
-        later step.
+        The same step runs here, on a throwaway pool.  Then, where steps will be replayed from
+        CUDA graphs, the widest ones the configuration allows (every sequence slot taken, block
+        tables for `max_model_len`; once decoding, once beside the longest prompt portion a graph
+        takes) are captured: what the graphs hold (their shared logits buffer and their memory
+        pool, which the widest graphs size) stays allocated beside every later step.
         """
         cfg, page = self.scheduler_config, self.cache_config.block_size
         device = self.device
         seqs = min(cfg.max_num_seqs, cfg.max_num_batched_tokens)
         each = max(1, min(cfg.max_num_batched_tokens // seqs, cfg.max_model_len - 1, cfg.prefill_chunk or (1 << 30)))
-        pages = seqs * -(-(each + 1) // page) + 1
+        limit = StepRunner.__init__.__kwdefaults__["graph_max_tokens"]
+        portion = max(0, min(limit - (seqs - 1), cfg.max_model_len - each - 3, cfg.prefill_chunk or limit))
+        pages = seqs * -(-(each + 2) // page) + -(-portion // page) + 2
         _, manager, storage = build_cache(self.model, page, pages, caching=False, num_state_slots=max(state_slots, 1))
         eager = StepRunner(self.model, manager, storage, cuda_graphs=False)
         sampler = Sampler(self.model.rt.ops, device, 0)
@@ -180,8 +182,21 @@ class LLM:
             for e in entries:
                 manager.commit(e.seq_id, each)
                 manager.extend(e.seq_id, [0])
-            replayed._capture([StepEntry(i, [0], [0]) for i in range(seqs)], StepRunner.bucket(seqs),
-                              list(replayed._graph_widths))
+            widest_tables = tuple(replayed._graph_widths)
+            batch = StepRunner.bucket(seqs)
+            replayed._capture([StepEntry(i, [0], [0]) for i in range(seqs)], StepShape(batch, batch, 0, 1, True, widest_tables))
+            if portion > 1:
+                # ... and the largest step with a prompt portion that is replayed from a graph
+                mixed = []
+                for i in range(seqs):
+                    manager.commit(i, 1)
+                    fed = [0] * (portion if i == 0 else 1)
+                    manager.extend(i, fed)
+                    mixed.append(StepEntry(i, fed, [len(fed) - 1]))
+                shape = replayed.graph_shape(mixed)
+                if shape is not None:
+                    replayed._capture(mixed, StepShape(shape.tokens, shape.seqs, shape.portions, shape.max_q, seqs > 1,
+                                                       widest_tables))
             torch.cuda.synchronize(device)
             torch.cuda.empty_cache()             # what the capture's eager run cached goes; what the graphs hold stays
             graphs_held = max(0, torch.cuda.memory_reserved(device) - before)

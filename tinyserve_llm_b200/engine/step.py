@@ -66,7 +66,9 @@ class StepContext:
         lens = [b - a for a, b in zip(host.cu_q, host.cu_q[1:])]
         self.max_q_len = max(lens, default=0)     # which attention kernels a step needs is decided on the host
         self.min_q_len = min(lens, default=0)
-        self.max_ctx_len = max(host.ctx_lens, default=0)   # an upper bound; a decode graph sets its bucket's bound
+        self.max_ctx_len = max(host.ctx_lens, default=0)   # an upper bound; a replayed step sets its shape's bound
+        # the split-key decode kernels size their grid and scratch by the longest request that feeds one token
+        self.max_decode_ctx_len = max((c for c, n in zip(host.ctx_lens, lens) if n == 1), default=0)
         self.scratch: dict = {}                   # per-step scratch buffers parts share (keyed by purpose and size)
 
     def binding(self, entry: RunEntry) -> EntryBinding | None:
@@ -83,36 +85,70 @@ def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
 
-class _DecodeGraph:
-    """A captured decode step for one batch size and one bound on the requests' pages: static index buffer in, static logits out."""
+def _power_of_two(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+@dataclass(frozen=True)
+class StepShape:
+    """
+    The sizes a step replayed from a CUDA graph is padded to: what its kernels' grids and its
+    buffers are sized by.  Real tokens come first, then padding rows (seq_of_token = -1); real
+    requests first, then padding requests that feed nothing; the list of prompt portions is
+    padded with -1.
+    """
+
+    tokens: int                 # rows of the flat batch
+    seqs: int                   # requests; also the number of logits rows the graph computes
+    portions: int               # entries of the list of requests that feed more than one token (0: none)
+    max_q: int                  # bound on the longest portion (1: every request feeds one token)
+    decodes: bool               # some request feeds exactly one token: the split-key kernels run
+    widths: tuple[int, ...]     # block-table width per layer group
+
+
+class _StepGraph:
+    """A captured step of one shape: static index buffer in, rows of the runner's static logits buffer out."""
 
     def __init__(self, graph: torch.cuda.CUDAGraph, index_buffer: torch.Tensor, logits: torch.Tensor,
-                 widths: list[int], launches: int) -> None:
+                 shape: StepShape, launches: int) -> None:
         self.graph = graph
         self.index_buffer = index_buffer
         self.logits = logits
-        self.widths = widths
+        self.shape = shape
+        self.widths = list(shape.widths)
         self.launches = launches       # kernels of the engine's own library inside the graph
 
 
 class StepRunner:
     """
-    `cuda_graphs`: steps in which every request feeds one token (decoding) are replayed from a CUDA
-    graph, when every part of the model is graph safe.  A graph is captured per bucket of the batch size
-    and of the pages the step's longest request holds (both powers of two): the attention's grid
-    covers what the block tables can hold, so a graph sized for the longest context the engine allows
-    would make every step pay for it (64 requests of 512 tokens: 1.26 ms a step with tables for 4,096
-    tokens, 3.4 ms with tables for 131,072).  The logits such a step returns live in one static buffer
-    that all graphs write ([largest batch bucket, vocab] float32, allocated at the first capture) and are
-    overwritten by the next decode step: consume them (sample, copy) before stepping again.  At most
-    `max_graphs` graphs are kept; the least recently used one goes first.  `table_pages` (per layer
-    group) stands in for the pools' page counts where the widest block table is worked out: a runner on
-    a small throwaway pool can then capture the graphs the real pool will need.
+    `cuda_graphs`: steps are replayed from CUDA graphs where every part of the model is graph safe.
+    A graph is captured per `StepShape`, the step's sizes rounded up to buckets:
+
+    * steps in which every request feeds one token (decoding): batch size in powers of two, block
+      tables as wide as the step's longest request needs (1, 2, 3, 4, 6, 8, 12, ... pages: the
+      attention's grid covers what the tables can hold, and tables for the longest context the
+      engine allows made 64 requests of 512 tokens cost 3.4 ms a step instead of 1.26);
+    * steps with prompt portions of up to `graph_max_tokens` tokens in all: tokens in multiples of
+      64 (128 from 512 on), requests, portions and the longest portion in powers of two.  Launched
+      kernel by kernel such a step costs about 2 ms of host time whatever its size, more than its
+      device time below a few hundred tokens.  A shape is captured when it is met the second time.
+
+    Larger steps, steps that want more logits rows than they have requests, and models with a part
+    that is not graph safe run eagerly.  The logits a replayed step returns live in one static
+    buffer that all graphs write ([largest batch bucket, vocab] float32, allocated at the first
+    capture) and are overwritten by the next replayed step: consume them (sample, copy) before
+    stepping again.  At most `max_graphs` graphs are kept; the least recently used one goes first.
+    `table_pages` (per layer group) stands in for the pools' page counts where the widest block
+    table is worked out: a runner on a small throwaway pool can then capture the graphs the real
+    pool will need.
     """
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: DeviceCacheStorage, *,
                  cuda_graphs: bool = True, max_decode_batch: int = 256, max_model_len: int | None = None,
-                 max_graphs: int = 48, table_pages: Sequence[int] | None = None) -> None:
+                 max_graphs: int = 64, table_pages: Sequence[int] | None = None, graph_max_tokens: int = 1024) -> None:
         self.model = model
         self.manager = manager
         self.storage = storage
@@ -123,14 +159,16 @@ class StepRunner:
         self._staged.record()
         self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
         self.max_decode_batch = max_decode_batch
+        self.graph_max_tokens = graph_max_tokens
         longest = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
         pool_pages = list(table_pages) if table_pages is not None else [pool.num_pages for pool in manager.pools]
         self._graph_widths = [max(1, min(pages, -(-longest // manager.page_tokens))) for pages in pool_pages]
         self._graph_logits: torch.Tensor | None = None   # [largest batch bucket, vocab] float32, shared by all graphs
-        self._graphs: dict[tuple, _DecodeGraph] = {}    # (batch bucket, table widths) -> graph, least recently used first
+        self._graphs: dict[StepShape, _StepGraph] = {}   # least recently used first
+        self._met: dict[StepShape, int] = {}             # shapes with portions seen so far and not captured yet
         self.max_graphs = max_graphs
         self._graph_pool = None                          # the graphs' intermediates share one memory pool
-        self.last_graph: _DecodeGraph | None = None
+        self.last_graph: _StepGraph | None = None
         self.graph_replays = 0
 
     # ------------------------------------------------------------------ packing
@@ -168,91 +206,125 @@ class StepRunner:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.seq_id!r}: wanted place {w} outside its {n} tokens")
 
-    def _pack(self, entries: Sequence[StepEntry], pad_to: int | None = None,
-              widths: list[int] | None = None, into: torch.Tensor | None = None) -> StepContext:
+    def _index_data(self, entries: Sequence[StepEntry], shape: StepShape | None) -> tuple[list[int], list[int], dict]:
         """
-        Index data of the step in one pinned buffer, one copy to the device.  `pad_to` (decode
-        graphs) pads the batch to a fixed number of single-token requests, padding rows marked by
-        seq_of_token = -1, and asks for the logits of every row; `into` is the static device buffer.
+        The step's index data as one list of int32 words in sections (each padded to 16 bytes):
+        token ids, positions, request of each token, offsets of the requests' tokens, lengths after
+        this step, wanted rows, state slots, one block table per layer group, and the requests
+        that feed more than one token.  With `shape`, every section is padded to the shape's size.
+        Returns (words, offset of each section, sizes).
         """
-        mgr = self.manager
-        ids: list[int] = []
-        positions: list[int] = []
-        seq_of_token: list[int] = []
-        cu_q, start, ctx_lens, rows, slots, seq_ids = [0], [], [], [], [], []
-        for s, e in enumerate(entries):
-            state = mgr.seqs[e.seq_id]
-            n = len(e.tokens)
-            first = state.committed
-            ids.extend(e.tokens if e.feed < 0 else (-(e.feed + 2),))
-            positions.extend(range(first, first + n))
-            seq_of_token.extend([s] * n)
-            rows.extend(cu_q[-1] + w for w in e.want)
-            cu_q.append(cu_q[-1] + n)
-            start.append(first)
-            ctx_lens.append(first + n)
-            slots.append(state.state_slot)
-            seq_ids.append(e.seq_id)
-        groups = len(mgr.pools)
-        if pad_to is not None:
-            extra = pad_to - len(entries)
-            ids.extend([0] * extra)
-            positions.extend([0] * extra)
-            seq_of_token.extend([-1] * extra)
-            cu_q.extend(range(cu_q[-1] + 1, cu_q[-1] + 1 + extra))
-            ctx_lens.extend([0] * extra)
-            slots.extend([-1] * extra)
-            rows = list(range(pad_to))
+        seqs = self.manager.seqs
+        states = [seqs[e.seq_id] for e in entries]
+        n = len(entries)
+        groups = len(self.manager.pools)
+        if all(len(e.tokens) == 1 for e in entries):            # decoding: no loop over tokens
+            first = [st.committed for st in states]
+            ids = [e.tokens[0] if e.feed < 0 else -(e.feed + 2) for e in entries]
+            positions = first
+            seq_of_token = list(range(n))
+            cu_q = list(range(n + 1))
+            ctx_lens = [f + 1 for f in first]
+            rows = [i for i, e in enumerate(entries) if len(e.want)]
+            portions: list[int] = []
         else:
-            widths = [max(1, max(len(mgr.seqs[e.seq_id].tables[g]) for e in entries)) for g in range(groups)]
-        T, S, R = len(ids), len(ctx_lens), len(rows)
+            ids, positions, seq_of_token, cu_q, ctx_lens, rows, portions = [], [], [], [0], [], [], []
+            for s, (e, st) in enumerate(zip(entries, states)):
+                k = len(e.tokens)
+                begin = st.committed
+                ids.extend(e.tokens if e.feed < 0 else (-(e.feed + 2),))
+                positions.extend(range(begin, begin + k))
+                seq_of_token.extend([s] * k)
+                at = cu_q[-1]
+                rows.extend(at + w for w in e.want)
+                cu_q.append(at + k)
+                ctx_lens.append(begin + k)
+                if k > 1:
+                    portions.append(s)
+        slots = [st.state_slot for st in states]
+        T, R, P = len(ids), len(rows), len(portions)
+        if shape is None:
+            widths = [max(1, max(len(st.tables[g]) for st in states)) for g in range(groups)]
+            S = n
+        else:
+            widths, S = list(shape.widths), shape.seqs
+            if T > shape.tokens or n > S or R > S or P > shape.portions:
+                raise ValueError("the step does not fit the shape it was bucketed into")
+            pad = shape.tokens - T
+            ids = ids + [0] * pad
+            positions = positions + [0] * pad
+            seq_of_token = seq_of_token + [-1] * pad
+            cu_q = cu_q + [T] * (S - n)                          # padding requests feed nothing
+            ctx_lens = ctx_lens + [0] * (S - n)
+            slots = slots + [-1] * (S - n)
+            rows = rows + [0] * (S - R)
+            portions = portions + [-1] * (shape.portions - P)
         sections = [ids, positions, seq_of_token, cu_q, ctx_lens, rows, slots]
         for g in range(groups):
             flat: list[int] = []
             width = widths[g]
-            for e in entries:
-                t = mgr.seqs[e.seq_id].tables[g]
+            for e, st in zip(entries, states):
+                t = st.tables[g]
                 if len(t) > width:
                     raise ValueError(f"request {e.seq_id!r} holds {len(t)} pages; the step was built for {width}")
                 flat.extend(t)
                 if len(t) < width:
                     flat.extend([-1] * (width - len(t)))
-            if S > len(entries):
-                flat.extend([-1] * (width * (S - len(entries))))
+            if S > n:
+                flat.extend([-1] * (width * (S - n)))
             sections.append(flat)
-        portions = [s for s, e in enumerate(entries) if len(e.tokens) > 1]
         sections.append(portions)
-        # one list, one conversion, one copy into the pinned buffer, one copy to the device
-        offsets, packed = [], []
+        offsets, words = [], []
         for sec in sections:
-            offsets.append(len(packed))
-            packed.extend(sec)
+            offsets.append(len(words))
+            words.extend(sec)
             pad = _pad4(max(len(sec), 1)) - len(sec)
             if pad:
-                packed.extend([0] * pad)
-        total = len(packed)
+                words.extend([0] * pad)
+        sizes = dict(tokens=len(ids), seqs=S, rows=len(rows), portions=len(portions), widths=widths, real_tokens=T,
+                     real_seqs=n, real_rows=R, real_portions=P, cu_q=cu_q, ctx_lens=ctx_lens, slots=slots)
+        return words, offsets, sizes
+
+    def _upload(self, words: list[int], into: torch.Tensor | None) -> torch.Tensor:
+        """One conversion, one copy into the pinned buffer, one copy to the device (into a graph's static buffer, if given)."""
+        total = len(words)
         if self._staging is None or self._staging.numel() < total:
             self._staging = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
         else:
             self._staged.synchronize()                  # the previous step's copy has read the buffer
         host = self._staging
-        host[:total] = torch.tensor(packed, dtype=torch.int32)
+        host[:total] = torch.tensor(words, dtype=torch.int32)
         if into is None:
             dev = host[:total].to(self.device, non_blocking=True)
         else:
             dev = into
             dev[:total].copy_(host[:total], non_blocking=True)
         self._staged.record()
+        return dev
 
-        ctx = StepContext(self, T, S, HostView(seq_ids, cu_q, start, ctx_lens, slots))
-        ctx.index_words = total
-        if pad_to is not None:                    # a graph is replayed for any lengths its tables can hold
-            ctx.max_ctx_len = max(w * mgr.page_tokens for w in widths) if widths else 0
-        view = lambda i, n: dev[offsets[i]:offsets[i] + n]  # noqa: E731
+    def _pack(self, entries: Sequence[StepEntry], shape: StepShape | None = None,
+              into: torch.Tensor | None = None) -> StepContext:
+        """The step's context: its index data on the device and what the host knows of it."""
+        words, offsets, sizes = self._index_data(entries, shape)
+        dev = self._upload(words, into)
+        n = sizes["real_seqs"]
+        cu_q, ctx_lens = sizes["cu_q"], sizes["ctx_lens"]
+        host = HostView([e.seq_id for e in entries], cu_q[:n + 1], [c - (b - a) for a, b, c in zip(cu_q, cu_q[1:], ctx_lens[:n])],
+                        ctx_lens[:n], sizes["slots"][:n])
+        ctx = StepContext(self, sizes["tokens"], sizes["seqs"], host)
+        ctx.index_words = len(words)
+        if shape is not None:                     # a graph is replayed for any step its shape can hold
+            bound = max(w * self.manager.page_tokens for w in shape.widths) if shape.widths else 0
+            ctx.max_q_len, ctx.min_q_len = shape.max_q, (1 if shape.decodes else shape.max_q)
+            ctx.max_ctx_len = ctx.max_decode_ctx_len = bound
+        T, S, R, P = sizes["tokens"], sizes["seqs"], sizes["rows"], sizes["portions"]
+        widths = sizes["widths"]
+        view = lambda i, k: dev[offsets[i]:offsets[i] + k]  # noqa: E731
         ctx.token_ids, ctx.positions, ctx.seq_of_token = view(0, T), view(1, T), view(2, T)
         ctx.cu_q, ctx.ctx_lens, ctx.rows, ctx.state_slots = view(3, S + 1), view(4, S), view(5, R), view(6, S)
+        groups = len(widths)
         ctx.tables = [view(7 + g, S * widths[g]).view(S, widths[g]) for g in range(groups)]
-        ctx.prefill_seqs = view(7 + groups, len(portions))
+        ctx.prefill_seqs = view(7 + groups, P)
         return ctx
 
     # ------------------------------------------------------------------ the step
@@ -267,8 +339,17 @@ class StepRunner:
         """
         self._validate(entries, device_tokens)
         self.model.rt.ops.check_device_errors()      # a bounded wait that ran out in an earlier step (host-visible word)
-        if self.cuda_graphs and len(entries) <= self.max_decode_batch and all(len(e.tokens) == 1 for e in entries):
-            return self._decode_step(entries, device_tokens)
+        shape = self.graph_shape(entries) if self.cuda_graphs else None
+        if shape is not None:
+            captured = self._graphs.pop(shape, None)
+            if captured is not None:
+                self._graphs[shape] = captured               # most recently used last
+                return self._replay(captured, entries, device_tokens)
+            if shape.portions == 0 or self._met.pop(shape, 0) >= 1:
+                return self._replay(self._capture(entries, shape, device_tokens), entries, None, launched=True)
+            if len(self._met) > 4 * self.max_graphs:
+                self._met.clear()
+            self._met[shape] = 1
         ctx = self._pack(entries)
         if device_tokens is not None:
             self.model.rt.ops.feed_tokens(ctx.token_ids, device_tokens)
@@ -277,17 +358,14 @@ class StepRunner:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.device)
         return self.model.logits(x, residual, ctx.rows)
 
-    # ------------------------------------------------------------------ decode steps from a CUDA graph
+    # ------------------------------------------------------------------ steps from CUDA graphs
     @staticmethod
     def bucket(n: int) -> int:
-        b = 1
-        while b < n:
-            b *= 2
-        return b
+        return _power_of_two(n)
 
     @staticmethod
     def width_bucket(pages: int) -> int:
-        """Block-table widths of decode graphs: 1, 2, 3, 4, 6, 8, 12, 16, 24, ... (at most half again what is needed)."""
+        """Block-table widths of graphs: 1, 2, 3, 4, 6, 8, 12, 16, 24, ... (at most half again what is needed)."""
         b = 1
         while b < pages:
             if b >= 2 and b + b // 2 >= pages:
@@ -295,89 +373,62 @@ class StepRunner:
             b *= 2
         return b
 
-    def _decode_step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
-        size = self.bucket(len(entries))
-        seqs = self.manager.seqs
-        widths = tuple(min(limit, self.width_bucket(max(len(seqs[e.seq_id].tables[g]) for e in entries)))
+    def graph_shape(self, entries: Sequence[StepEntry]) -> StepShape | None:
+        """The shape this step would be replayed in; None where it runs eagerly."""
+        n = len(entries)
+        if n > self.max_decode_batch:
+            return None
+        tokens = rows = portions = longest = 0
+        decodes = False
+        for e in entries:
+            k = len(e.tokens)
+            tokens += k
+            rows += len(e.want)
+            if k > 1:
+                portions += 1
+                longest = max(longest, k)
+            else:
+                decodes = True
+        seqs = _power_of_two(n)
+        if rows > seqs:
+            return None
+        states = self.manager.seqs
+        widths = tuple(min(limit, self.width_bucket(max(len(states[e.seq_id].tables[g]) for e in entries)))
                        for g, limit in enumerate(self._graph_widths))
-        captured = self._graphs.pop((size, widths), None)
-        if captured is not None:
-            self._graphs[(size, widths)] = captured          # most recently used last
-        if captured is None:
-            captured = self._capture(entries, size, list(widths), device_tokens)
-        else:
-            self._refill(entries, size, captured)
+        if portions == 0:
+            return StepShape(seqs, seqs, 0, 1, True, widths)
+        if tokens > self.graph_max_tokens:
+            return None
+        step = 64 if tokens <= 512 else 128
+        padded = -(-tokens // step) * step
+        return StepShape(padded, seqs, _power_of_two(portions), min(padded, max(64, _power_of_two(longest))), decodes, widths)
+
+    def _replay(self, captured: _StepGraph, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None,
+                launched: bool = False) -> torch.Tensor:
+        if not launched:
+            words, _, _ = self._index_data(entries, captured.shape)
+            self._upload(words, captured.index_buffer)
             if device_tokens is not None:
-                self.model.rt.ops.feed_tokens(captured.index_buffer[:size], device_tokens)
+                self.model.rt.ops.feed_tokens(captured.index_buffer[:captured.shape.tokens], device_tokens)
             captured.graph.replay()
             self.model.rt.ops.launches += captured.launches
         self.graph_replays += 1
         self.last_graph = captured
-        wanted = [i for i, e in enumerate(entries) if len(e.want)]
-        if len(wanted) == len(entries):
-            return captured.logits[:len(entries)]
-        if not wanted:
-            return captured.logits[:0]
-        return captured.logits.index_select(0, torch.tensor(wanted, dtype=torch.int64, device=self.device))
+        return captured.logits[:sum(len(e.want) for e in entries)]
 
-    def _refill(self, entries: Sequence[StepEntry], size: int, captured: _DecodeGraph) -> None:
-        """
-        The index data of a decode step straight into the graph's static buffer: the same layout
-        `_pack` produces for `pad_to=size`, without building a context nobody reads.
-        """
-        seqs = self.manager.seqs
-        n, extra = len(entries), size - len(entries)
-        states = [seqs[e.seq_id] for e in entries]
-        first = [st.committed for st in states]
-        packed: list[int] = []
-
-        def section(values: list[int]) -> None:
-            packed.extend(values)
-            pad = _pad4(max(len(values), 1)) - len(values)
-            if pad:
-                packed.extend([0] * pad)
-
-        section([e.tokens[0] if e.feed < 0 else -(e.feed + 2) for e in entries] + [0] * extra)    # token ids
-        section(first + [0] * extra)                                              # positions
-        section(list(range(n)) + [-1] * extra)                                    # request of each token
-        section(list(range(size + 1)))                                            # offsets: one token each
-        section([f + 1 for f in first] + [0] * extra)                             # lengths after this step
-        section(list(range(size)))                                                # every row's logits
-        section([st.state_slot for st in states] + [-1] * extra)                  # state slots
-        for g, width in enumerate(captured.widths):
-            flat: list[int] = []
-            for st in states:
-                t = st.tables[g]
-                if len(t) > width:
-                    raise ValueError(f"a request holds {len(t)} pages; the decode graph was built for {width}")
-                flat.extend(t)
-                if len(t) < width:
-                    flat.extend([-1] * (width - len(t)))
-            flat.extend([-1] * (width * extra))
-            section(flat)
-        section([])                                                               # no prompt portions
-        total = len(packed)
-        if self._staging is None or self._staging.numel() < total:
-            self._staging = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
-        else:
-            self._staged.synchronize()
-        self._staging[:total] = torch.tensor(packed, dtype=torch.int32)
-        captured.index_buffer[:total].copy_(self._staging[:total], non_blocking=True)
-        self._staged.record()
-
-    def _capture(self, entries: Sequence[StepEntry], size: int, widths: list[int],
-                 device_tokens: torch.Tensor | None = None) -> _DecodeGraph:
-        probe = self._pack(entries, pad_to=size, widths=widths)
-        index_buffer = torch.empty(probe.index_words, dtype=torch.int32, device=self.device)
-        ctx = self._pack(entries, pad_to=size, widths=widths, into=index_buffer)
+    def _capture(self, entries: Sequence[StepEntry], shape: StepShape,
+                 device_tokens: torch.Tensor | None = None) -> _StepGraph:
+        words, _, _ = self._index_data(entries, shape)
+        index_buffer = torch.empty(len(words), dtype=torch.int32, device=self.device)
+        ctx = self._pack(entries, shape, into=index_buffer)
         if device_tokens is not None:
             self.model.rt.ops.feed_tokens(ctx.token_ids, device_tokens)
-        # once eagerly: libraries create their handles and workspaces outside the capture; the
-        # step's keys and values are written by this run and again, identically, by the replay
         if self._graph_logits is None:
             self._graph_logits = torch.empty((self.bucket(self.max_decode_batch), self.model.spec.vocab_size),
                                              dtype=torch.float32, device=self.device)
-        out = self._graph_logits[:size]
+        out = self._graph_logits[:shape.seqs]
+        # once eagerly: libraries create their handles and workspaces outside the capture; the
+        # step's keys and values are written by this run and again, identically, by the replay
         x, residual = self.model.forward(ctx)
         self.model.logits(x, residual, ctx.rows, out=out)
         torch.cuda.synchronize(self.device)
@@ -391,8 +442,8 @@ class StepRunner:
             logits = self.model.logits(x, residual, ctx.rows, out=out)
         launches = ops.launches - before
         graph.replay()
-        captured = _DecodeGraph(graph, index_buffer, logits, widths, launches)
+        captured = _StepGraph(graph, index_buffer, logits, shape, launches)
         while len(self._graphs) >= self.max_graphs:
             self._graphs.pop(next(iter(self._graphs)))
-        self._graphs[(size, tuple(widths))] = captured
+        self._graphs[shape] = captured
         return captured

@@ -341,9 +341,12 @@ class Ops:
                 if ctx.min_q_len > 1:
                     return out
                 max_q_len = 1
+            # the decode grid and scratch follow the longest request that feeds ONE token: a long prompt portion beside
+            # short decodes must not size them (a bare context may not say, then the longest request of all does)
+            decode_ctx = getattr(ctx, "max_decode_ctx_len", ctx.max_ctx_len)
             if ctx.min_q_len <= 1:
                 floats = self.lib.ts_attention_bf16_scratch_floats(num_seqs, nh, hd,
-                                                                   ctx.max_ctx_len)
+                                                                   decode_ctx)
                 key = ("attention", floats)
                 scratch = ctx.scratch.get(key)
                 if scratch is None:
@@ -352,7 +355,7 @@ class Ops:
                        binding.page_stride, binding.entry_offset, binding.page_tokens,
                        binding.num_pages, _ptr(binding.block_table), binding.table_width,
                        _ptr(ctx.cu_q), _ptr(ctx.ctx_lens), num_seqs, max_q_len,
-                       min(ctx.min_q_len, max_q_len), ctx.max_ctx_len, nh, nkv, hd,
+                       min(ctx.min_q_len, max_q_len), decode_ctx, nh, nkv, hd,
                        scale, window, _ptr(scratch), floats, _ptr(prefill_seqs),
                        num_prefill, _stream())
             if ctx.min_q_len <= 1:
