@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import argparse
 import contextlib
+import dataclasses
 import json
 import os
 import statistics
@@ -196,7 +197,7 @@ def run_ours(args) -> dict:
     steps, warmup = args.steps, max(args.warmup, 3)
     max_len = CONTEXT + steps + warmup + 64 + 512
     pages = 66 * (-(-max_len // PAGE) + 1) + 16
-    llm = LLM(folder, SchedulerConfig(max_model_len=max_len, max_num_seqs=64, max_num_batched_tokens=8192,
+    llm = LLM(folder, SchedulerConfig(max_model_len=max_len, max_num_seqs=96, max_num_batched_tokens=8192,
                                       prefill_chunk=2048, watermark=0.0),
               CacheConfig(block_size=PAGE, caching=False), dtype="bfloat16", num_blocks=pages, seed=0,
               random_weights_seed=0)
@@ -339,6 +340,50 @@ def run_ours(args) -> dict:
         cache.commit(("mixed", 0), PREFILL_TOKENS)
         cache.release(("mixed", 0))
 
+    # prompts that arrive while 64 requests decode, in portions of 64 tokens: through the entry point (wall clock,
+    # host token ids in and out) and the same step on the device alone
+    chunk_tokens, arriving_prompt = 64, 512
+    with held_contexts(64, point_context) as decodes:
+        arriving = prompts(1, arriving_prompt)[0]
+        assert cache.admit(("chunk", 0), arriving[:256])
+        runner.step([StepEntry(("chunk", 0), arriving[:256], [])])
+        cache.commit(("chunk", 0), 256)
+        cache.extend(("chunk", 0), arriving[256:256 + chunk_tokens])
+        chunk_entries = decodes + [StepEntry(("chunk", 0), arriving[256:256 + chunk_tokens], [])]
+        for _ in range(3):
+            runner.step(chunk_entries)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(10):
+            runner.step(chunk_entries)
+        end.record()
+        torch.cuda.synchronize()
+        chunk_device_ms = begin.elapsed_time(end) / 10
+        cache.commit(("chunk", 0), chunk_tokens)
+        cache.release(("chunk", 0))
+    sched = llm.scheduler
+    saved_config = sched.config
+    sched.config = dataclasses.replace(saved_config, prefill_chunk=chunk_tokens)
+    chunk_steps = 64
+    start_decoding(64, point_context, chunk_steps + 200)
+    one_token = SamplingParams(max_tokens=1, temperature=0.0, ignore_eos=True)
+    llm.add_request(prompts(1, arriving_prompt)[0], one_token)
+    for _ in range(24):                                         # the shapes of these steps are captured meanwhile
+        if llm.step():
+            llm.add_request(prompts(1, arriving_prompt)[0], one_token)
+    torch.cuda.synchronize()
+    fed_before = sched.stats().prefill_tokens + sched.stats().decode_tokens
+    t0 = time.perf_counter()
+    for _ in range(chunk_steps):
+        if llm.step():                                          # the arriving request is done: the next one arrives
+            llm.add_request(prompts(1, arriving_prompt)[0], one_token)
+    torch.cuda.synchronize()
+    chunk_seconds = time.perf_counter() - t0
+    chunk_fed = sched.stats().prefill_tokens + sched.stats().decode_tokens - fed_before
+    sched.config = saved_config
+    finish_all()
+
     value = BATCH / ms * 1e3
     moved = weight_bytes(cfg, layers) + kv_bytes(cfg, layers, BATCH, CONTEXT)
     achieved = moved / (ms * 1e-3) / 1e9
@@ -368,6 +413,10 @@ def run_ours(args) -> dict:
         "points": points,
         "mixed": {"decodes": 64, "prefill_tokens": PREFILL_TOKENS, "ms": round(mixed_ms, 3),
                   "value": round((64 + PREFILL_TOKENS) / mixed_ms * 1e3, 1), "unit": "tokens/s"},
+        "chunked": {"decodes": 64, "portion_tokens": chunk_tokens, "prompt_tokens": arriving_prompt, "steps": chunk_steps,
+                    "device_ms": round(chunk_device_ms, 3), "e2e_ms": round(chunk_seconds / chunk_steps * 1e3, 3),
+                    "e2e_over_device": round(chunk_seconds / chunk_steps * 1e3 / chunk_device_ms, 3),
+                    "value": round(chunk_fed / chunk_seconds, 1), "unit": "tokens/s fed (decoded + prompt), end to end"},
         "e2e": {"value": round(BATCH * steps / e2e_seconds, 1), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": BATCH * 4},
         "gpu_launches": launches,

@@ -31,8 +31,8 @@ class FakeStorage:
         seq = manager.seqs[seq_id]
         B = self.page_tokens
         for pos in range(seq.committed, seq.reserved):
-            for g, table in enumerate(seq.tables):
-                page = table[pos // B]
+            for g, pool in enumerate(manager.pool_of_group):          # every layer group writes its own tensors
+                page = seq.tables[pool][pos // B]
                 assert page >= 0, "a token is written into a page that was given back"
                 self.slots[g][page][pos % B] = seq.tokens[pos]
             if seq.state_slot >= 0:
@@ -46,34 +46,46 @@ def layout_of(page_tokens=4, windows=(0,), state_bytes=0) -> CacheLayout:
 
 
 def check_invariants(manager: CacheManager, storage: FakeStorage) -> None:
+    """
+    No page lost, held twice or freed twice; the record of cached pages says what the pages hold;
+    every token a request may still read is where its table says; windows and state slots as promised.
+    """
     B = manager.page_tokens
-    for g, pool in enumerate(manager.pools):
-        holders = Counter(p for s in manager.seqs.values() for p in s.tables[g] if p >= 0)
+    index = manager.index
+    for p, pool in enumerate(manager.pools):
+        holders = Counter(page for s in manager.seqs.values() for page in s.tables[p] if page >= 0)
         for page in range(pool.num_pages):
-            assert pool.refs[page] == holders.get(page, 0), f"group {g} page {page}: ref {pool.refs[page]} vs holders"
-        free = list(pool.free) + list(pool.free_cached)
+            assert pool.refs[page] == holders.get(page, 0), f"pool {p} page {page}: ref {pool.refs[page]} vs holders"
+        free = pool.blank_pages() + pool.idle_pages()
         assert len(free) == len(set(free)), "a page is free twice"
-        assert set(free) == {p for p in range(pool.num_pages) if pool.refs[p] == 0}, "a page is lost or held while free"
-        for page in pool.free_cached:
-            assert g == 0 and page in manager.tree.nodes
-        for page in pool.free:
-            assert g != 0 or page not in manager.tree.nodes
-    # the tree: chained, partial pages are leaves, contents are what the tree says, held pages have held parents
-    refs0 = manager.pools[0].refs if manager.pools else []
-    for page, node in manager.tree.nodes.items():
-        assert node.page == page and 0 < len(node.tokens) <= B
-        assert node.parent.children[node.tokens] is node
-        if len(node.tokens) < B:
-            assert not node.children, "a partly filled page has children"
-        assert tuple(storage.slots[0][page][:len(node.tokens)]) == node.tokens, "cached page does not hold its tokens"
-        if refs0[page] > 0 and node.parent.page >= 0:
-            assert refs0[node.parent.page] > 0, "a held page's parent is free"
+        assert set(free) == {page for page in range(pool.num_pages) if pool.refs[page] == 0}, "a page is lost or held while free"
+        assert pool.available() == len(free)
+        for page in pool.idle_pages():
+            assert pool.index is not None and page in pool.index.by_page, "an idle page is not on record"
+        for page in pool.blank_pages():
+            assert pool.index is None or page not in pool.index.by_page, "a blank page is on record"
+    if index is not None:
+        refs = manager.pools[manager.shared].refs
+        for page, entry in index.by_page.items():
+            assert entry.page == page and 0 < len(entry.tokens) <= B
+            assert entry in entry.before.after
+            if len(entry.tokens) < B:
+                assert not entry.after, "a partly filled page is continued"
+            keys = [e.tokens for e in entry.after]
+            assert keys == sorted(keys) and len(set(keys)) == len(keys), "the pages after a page are out of order"
+            for g in manager.groups_of_pool[manager.shared]:
+                assert tuple(storage.slots[g][page][:len(entry.tokens)]) == entry.tokens, "cached page does not hold its tokens"
+            if refs[page] > 0 and entry.before.page >= 0:
+                assert refs[entry.before.page] > 0, "a held page continues from a free one"
+        # every idle page can be reached by evicting from the ends: an idle page has no held page behind it
+        for page in manager.pools[manager.shared].idle_pages():
+            assert all(refs[e.page] == 0 for e in index.by_page[page].after)
     used_slots = [s.state_slot for s in manager.seqs.values() if s.state_slot >= 0]
     assert len(used_slots) == len(set(used_slots)), "two requests share a state slot"
     assert not set(used_slots) & set(manager._free_slots), "a state slot is free while in use"
     for seq in manager.seqs.values():
         for g, group in enumerate(manager.layout.groups):
-            table = seq.tables[g]
+            table = seq.tables[manager.pool_of_group[g]]
             assert len(table) == -(-seq.reserved // B)
             first_needed = max(0, seq.committed - group.window + 1) if group.window else 0
             for pos in range(seq.committed):
@@ -86,8 +98,8 @@ def check_invariants(manager: CacheManager, storage: FakeStorage) -> None:
                 for i, page in enumerate(table):
                     if (i + 1) * B <= first_needed:
                         assert page == -1, "a page behind the window is still held"
-        if manager.caching:
+        if index is not None:
             for i in range(seq.committed // B):
-                assert seq.tables[0][i] in manager.tree.nodes, "a full committed page is not in the tree"
+                assert seq.tables[manager.shared][i] in index.by_page, "a full committed page is not on record"
         if seq.state_slot >= 0:
             assert storage.state[seq.state_slot] == seq.tokens[:seq.committed], "state does not follow the tokens"

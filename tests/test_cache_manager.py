@@ -9,7 +9,7 @@ import random
 import pytest
 
 from cache_fakes import FakeStorage, check_invariants, layout_of
-from tinyserve_llm_b200.cache import CacheFull, CacheManager, PrefixTree, TokenTrie, plan_layout
+from tinyserve_llm_b200.cache import CacheFull, CacheManager, PagePool, PrefixIndex, plan_layout, shared_run
 from tinyserve_llm_b200.parts.base import KVNeed
 
 
@@ -41,23 +41,71 @@ def decode(manager, storage, seq_id, token):
     check_invariants(manager, storage)
 
 
-# ----------------------------------------------------------------------------- trie and tree
-def test_trie_longest_run_and_discard():
-    trie, a, b = TokenTrie(), object(), object()
-    trie.add(a, (1, 2, 3))
-    trie.add(b, (1, 2, 9, 9))
-    assert trie.longest_run((1, 2, 3, 4)) == (3, {a})
-    assert trie.longest_run((1, 2)) == (2, {a, b})
-    assert trie.longest_run((7,)) == (0, set())
-    trie.discard(a, (1, 2, 3))
-    assert trie.longest_run((1, 2, 3)) == (2, {b})
+# ----------------------------------------------------------------------------- the index and the pool
+def test_shared_run_counts_leading_tokens():
+    assert shared_run((1, 2, 3), (1, 2, 3)) == 3 and shared_run((1, 2, 3), (1, 2, 9, 9)) == 2
+    assert shared_run((), (1,)) == 0 and shared_run((5,), (6,)) == 0 and shared_run((1, 2, 3, 4, 5, 6, 7), (1, 2, 3, 4, 5, 9, 7)) == 5
 
 
-def test_tree_never_matches_the_last_token():
-    tree = PrefixTree(4)
-    tree.publish(tree.root, 0, (1, 2, 3, 4))
-    assert tree.match([1, 2, 3, 4]).num_tokens == 3            # the last token is left to run
-    assert tree.match([1, 2, 3, 4, 5]).num_tokens == 4
+def test_the_nearest_pages_are_neighbours_in_the_sorted_list():
+    index = PrefixIndex(4)
+    a = index.file(index.root, 0, (1, 2, 3))
+    b = index.file(index.root, 1, (1, 2, 9, 9))
+    c = index.file(index.root, 2, (1, 5))
+    d = index.file(index.root, 3, (0, 7))
+    assert [e.tokens for e in index.root.after] == [(0, 7), (1, 2, 3), (1, 2, 9, 9), (1, 5)]
+    assert index.nearest(index.root, (1, 2, 3, 4)) == (3, [a])
+    run, pages = index.nearest(index.root, (1, 2))
+    assert run == 2 and set(pages) == {a, b}
+    assert index.nearest(index.root, (7,)) == (0, []) and index.nearest(index.root, (1, 6)) [0] == 1
+    assert set(index.nearest(index.root, (1, 6))[1]) == {a, b, c}
+    index.drop(a)
+    assert index.nearest(index.root, (1, 2, 3)) == (2, [b]) and len(index) == 3 and d.before is index.root
+
+
+def test_lookup_never_takes_the_last_token_and_honours_a_limit():
+    index = PrefixIndex(4)
+    first = index.file(index.root, 0, (1, 2, 3, 4))
+    index.file(first, 1, (5, 6))
+    assert index.lookup([1, 2, 3, 4]).num_tokens == 3              # the last token is left to run (a run of 3 to copy)
+    assert index.lookup([1, 2, 3, 4, 5]).num_tokens == 4
+    whole = index.lookup([1, 2, 3, 4, 5, 6, 7])
+    assert whole.num_tokens == 6 and [p.page for p in whole.pages] == [0, 1] and whole.run == 0
+    assert index.lookup([1, 2, 3, 4, 5, 6, 7], limit=5).num_tokens == 5
+    assert index.lookup([1, 2, 3, 4, 5, 6, 7], limit=0).num_tokens == 0
+    partial = index.lookup([1, 2, 9, 9, 9])
+    assert partial.run == 2 and partial.pages == [] and [p.page for p in partial.starting_with_run] == [0]
+
+
+def test_a_page_that_gains_tokens_moves_in_the_order_and_meets_its_twin():
+    index = PrefixIndex(4)
+    a = index.file(index.root, 0, (1, 2))
+    b = index.file(index.root, 1, (1, 2, 0, 5))
+    assert index.file(index.root, 7, (1, 2)) is a                 # the same tokens again: the page on record is kept
+    assert index.lengthen(a, (1, 2, 3)) is a and [e.page for e in index.root.after] == [1, 0]
+    assert index.lengthen(a, (1, 2, 3, 4)) is a
+    c = index.file(index.root, 2, (1, 2, 0))
+    assert index.lengthen(c, (1, 2, 0, 5)) is b and c.tokens == (1, 2, 0)
+
+
+def test_the_pool_evicts_the_stalest_end_of_a_chain_and_wakes_idle_pages():
+    index = PrefixIndex(2)
+    pool = PagePool(4, index)
+    pages = [pool.take() for _ in range(3)]
+    assert pages == [0, 1, 2] and pool.available() == 1
+    first = index.file(index.root, 0, (1, 2))
+    second = index.file(first, 1, (3, 4))
+    for page in (2, 1, 0):                                         # from the end, as a released request does
+        pool.let_go(page)
+    assert pool.blank_pages() == [3, 2] and sorted(pool.idle_pages()) == [0, 1] and pool.available() == 4
+    assert [pool.take(), pool.take()] == [2, 3]
+    assert pool.take() == 1 and second.page not in index.by_page and pool.evictions == 1   # the end of the chain first
+    pool.hold(0)                                                   # an idle page taken up again keeps its record
+    assert pool.refs[0] == 1 and not pool.is_idle(0) and index.by_page[0] is first
+    with pytest.raises(CacheFull):
+        pool.take()
+    pool.let_go(0)
+    assert pool.take() == 0 and len(index) == 0
 
 
 # ----------------------------------------------------------------------------- scenarios
@@ -116,7 +164,7 @@ def test_eviction_takes_the_least_recently_released_leaf():
     run(m, s, "a", [1, 2, 3, 4, 5, 6, 7, 8, 9])                # pages: [1234] [5678] [9]
     m.release("a")
     run(m, s, "b", [50, 51, 52, 53, 54])                       # takes the free page, then evicts the tail [9]
-    assert m.counters.evictions == 1
+    assert m.stats().evictions == 1
     assert m.admission_cost([1, 2, 3, 4, 5, 6, 7, 8, 9, 10]).prefill_tokens == 2    # [9] is gone, 8 remain
     m.release("b")
     check_invariants(m, s)
@@ -152,6 +200,22 @@ def test_two_groups_have_pages_of_their_own():
     m.release("x"), m.release("y")
     check_invariants(m, s)
     assert m.available_pages() == (8, 8)
+
+
+def test_groups_that_keep_all_keys_share_one_pool_and_prefix_reuse_survives():
+    m, s = make(pages=10, windows=(0, 0))                      # two layer groups of full attention
+    assert m.caching and len(m.pools) == 1 and m.pool_of_group == [0, 0]
+    run(m, s, "a", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
+    m.release("a")
+    assert m.admit("b", [1, 2, 3, 4, 5, 6, 77])
+    assert m.committed_tokens("b") == 6 and m.counters.partial_copies == 1
+    assert sorted(c[0] for c in s.copies) == [0, 1]            # the copied run is copied in both groups' tensors
+    s.run_step(m, "b")
+    m.commit("b", 1)
+    check_invariants(m, s)
+    m.fork("b", "c")
+    decode(m, s, "c", 5)                                       # copy on write, again in both groups
+    assert sorted(c[0] for c in s.copies) == [0, 0, 1, 1] and m.block_table("c", 0) == m.block_table("c", 1)
 
 
 def test_state_slots_are_taken_copied_and_given_back():
@@ -190,11 +254,11 @@ def test_layout_groups_entries_by_geometry():
 
 # ----------------------------------------------------------------------------- random workloads
 @pytest.mark.parametrize("seed", range(12))
-@pytest.mark.parametrize("kind", ["cached", "plain", "window", "state"])
+@pytest.mark.parametrize("kind", ["cached", "plain", "window", "state", "two_full"])
 def test_random_orders_of_requests_keep_the_contract(seed, kind):
     rng = random.Random(1000 * seed + len(kind))
     kwargs = {"cached": {}, "plain": {"caching": False}, "window": {"windows": (0, 7)},
-              "state": {"state_bytes": 8, "slots": 5}}[kind]
+              "state": {"state_bytes": 8, "slots": 5}, "two_full": {"windows": (0, 0)}}[kind]
     m, s = make(pages=rng.choice([6, 9, 14]), page_tokens=rng.choice([2, 4]), **kwargs)
     stems = [[rng.randrange(4) for _ in range(12)] for _ in range(3)]       # shared prefixes are likely
     live, next_id = {}, 0

@@ -66,21 +66,22 @@ class World:
         self.batches.append(batch)
         fed_on_device = {}
         if before is not None:
-            fed_on_device = {s.seq.seq_id: tokens[0] for s, tokens in zip(*before)}
+            fed_on_device = {s.seq.seq_id: tokens[0] for s, tokens in zip(*before) if tokens}
         sampled = []
         B = self.cache.page_tokens
         for seq, fed, num_samples in batch:
             state = self.cache.seqs[seq.seq_id]
             assert list(fed) == state.tokens[state.committed:], "fed tokens are not the reserved ones"
-            if before is None:
-                assert state.tokens == seq.all_token_ids[:state.reserved], "the cache holds other tokens than the sequence"
-                self.storage.run_step(self.cache, seq.seq_id)
+            if before is None or list(fed) != [PENDING_TOKEN]:
+                if before is None:
+                    assert state.tokens == seq.all_token_ids[:state.reserved], "the cache holds other tokens than the sequence"
+                self.storage.run_step(self.cache, seq.seq_id)        # tokens the host knows: a prompt portion, also in a step launched ahead
             else:
-                assert list(fed) == [PENDING_TOKEN] and state.reserved == state.committed + 1
+                assert state.reserved == state.committed + 1
                 pos = state.committed
                 self.storage.slots[0][state.tables[0][pos // B]][pos % B] = fed_on_device[seq.seq_id]
             history = [self.storage.slots[0][state.tables[0][p // B]][p % B] for p in range(state.reserved)]
-            first = not seq.output_token_ids and before is None
+            first = not seq.output_token_ids and seq.seq_id not in fed_on_device     # the first draw of a sequence
             sampled.append([next_token(history, i if first else 0) for i in range(num_samples)])
         return batch, sampled
 
@@ -251,13 +252,13 @@ def test_ranking_by_hit_then_wait_and_skip_until_waited():
     w.add([1, 2, 3, 4, 5, 6, 7, 8, 9], max_tokens=1)
     w.run_all()
     cold, warm = w.add([40, 41, 42, 43, 44], max_tokens=1), w.add([1, 2, 3, 4, 5, 6, 7, 8, 50], max_tokens=1)
-    ranked = [s.request_id for s, _, _ in w.scheduler._ranked_waiting(w.now)]
+    ranked = [c.seq.request_id for c in w.scheduler.waiting_by_rank(w.now)]
     assert ranked == [warm, cold]                               # the cache hit ranks first
     w2 = World(wait_weight=1.0)
     old = w2.add([1, 2, 3], max_tokens=1)
     w2.now = 10.0
     new = w2.add([4, 5, 6], max_tokens=1)
-    assert [s.request_id for s, _, _ in w2.scheduler._ranked_waiting(w2.now)] == [old, new]
+    assert [c.seq.request_id for c in w2.scheduler.waiting_by_rank(w2.now)] == [old, new]
     # a misfit is skipped while young, and blocks admission once it has waited max_skip_wait
     w3 = World(pages=12, max_skip_wait=5.0, caching=False)
     w3.add(range(24), max_tokens=16)                            # holds 6 of 12 pages and keeps decoding
@@ -352,10 +353,37 @@ def test_run_ahead_needs_a_queue_that_cannot_be_served_and_every_running_sequenc
     w.step()                                       # admits it beside the first one's decode
     assert len(w.scheduler.running) == 2 and w.launched_ahead == before + 1
 
+
+
+def test_run_ahead_carries_a_prompt_through_its_portions_into_decoding():
+    """A sequence still in its prompt feeds its next portion in the step launched ahead; where its prompt ends it goes on with the unknown token."""
     w = World(run_ahead=True, prefill_chunk=2)
+    a = w.add([1, 2, 3, 4, 5], max_tokens=3)
+    w.step()
+    assert w.launched_ahead == 1 and [s.token_ids for s in w.batches[-1]] == [[3, 4]]
+    done = w.run_all()
+    # portions [1 2] [3 4] [5], then two decode steps: every step but the last had its successor launched behind it
+    assert [len(b[0].token_ids) for b in w.batches] == [2, 2, 1, 1, 1] and w.launched_ahead == 4
+    assert [s.num_samples for b in w.batches for s in b] == [0, 0, 1, 1, 1]
+    assert _outputs(done, a) == [reference_output([1, 2, 3, 4, 5], 3)] and w.cache.stats().pages_in_use == 0
+    # a decoding sequence beside an arriving prompt: both go on in the steps launched ahead
+    w = World(run_ahead=True, prefill_chunk=3, max_num_batched_tokens=8)
+    first = w.add([7, 8, 9], max_tokens=8)
+    w.step()
+    second = w.add(list(range(20, 31)), max_tokens=2)
+    before = w.launched_ahead
+    w.step(), w.step()                                   # the first admits the arrival; behind it the mixed step is launched
+    assert w.launched_ahead >= before + 1
+    mixed = [b for b in w.batches if len(b) == 2 and {len(s.token_ids) for s in b} == {1, 3}]
+    assert mixed, [[s.token_ids for s in b] for b in w.batches]
+    done = w.run_all()
+    assert _outputs(done, first) == [reference_output([7, 8, 9], 8)]
+    assert _outputs(done, second) == [reference_output(list(range(20, 31)), 2)]
+    # prompts alone make up a step where prefills go first: nothing is launched behind it
+    w = World(run_ahead=True, prefill_chunk=2, step_mode="prefill_first")
     w.add([1, 2, 3, 4, 5], max_tokens=3)
     w.step()
-    assert w.launched_ahead == 0                   # a prompt portion samples nothing: the next step is not a decode
+    assert w.launched_ahead == 0
 
 
 def test_run_ahead_leaves_out_a_sequence_that_reaches_max_tokens():

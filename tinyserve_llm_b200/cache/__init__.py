@@ -1,6 +1,5 @@
 from tinyserve_llm_b200.cache.manager import (
     AdmissionCost,
-    CacheFull,
     CacheLayout,
     CacheManager,
     CacheStats,
@@ -8,9 +7,9 @@ from tinyserve_llm_b200.cache.manager import (
     NullStorage,
     plan_layout,
 )
-from tinyserve_llm_b200.cache.prefix_tree import PageNode, PrefixMatch, PrefixTree, TokenTrie
+from tinyserve_llm_b200.cache.pool import CacheFull, PagePool
+from tinyserve_llm_b200.cache.prefix_index import CachedPage, PrefixIndex, Reuse, shared_run
 from tinyserve_llm_b200.cache.storage import DeviceCacheStorage, EntryBinding
 
-__all__ = ["AdmissionCost", "CacheFull", "CacheLayout", "CacheManager", "CacheStats", "DeviceCacheStorage",
-           "EntryBinding", "GroupLayout", "NullStorage", "PageNode", "PrefixMatch", "PrefixTree", "TokenTrie",
-           "plan_layout"]
+__all__ = ["AdmissionCost", "CacheFull", "CacheLayout", "CacheManager", "CacheStats", "CachedPage", "DeviceCacheStorage",
+           "EntryBinding", "GroupLayout", "NullStorage", "PagePool", "PrefixIndex", "Reuse", "plan_layout", "shared_run"]

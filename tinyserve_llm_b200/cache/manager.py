@@ -4,32 +4,35 @@ state slot belongs to which request.  No tensor lives here; copies of page conte
 `storage` object (the device pools in production, a fake in the CPU tests) and are ordered on its
 stream.
 
-Pages.  A layer group (the cache entries whose mixers share kv heads, head size and window) has its
-own pool of fixed-size pages and, per request, its own block table.  A group that keeps all keys
-holds a request's pages until the request is released; a window group gives pages back as soon as
-every token in them is further than `window` behind the committed length, and marks them -1 in the
-table.  Released pages are reused.
+Pools.  Layer groups (the cache entries whose mixers share kv heads, head size and window) that
+keep all keys fill and empty in step with one another, so they share ONE pool of page ids and one
+block table per request: page p of a request is page p in each of these groups' tensors.  Every
+group with a window has a pool and a table of its own: it gives a page back as soon as every token
+in it is further than `window` behind the committed length, and marks it -1 in the table.
 
-Prefix reuse.  When there is exactly one group, it keeps all keys and nothing needs per-request
-state, released pages stay indexed in a prefix tree (cache/prefix_tree.py) until evicted, least
-recently released leaf first, and a new request attaches the longest cached prefix token by token:
-whole pages by reference, a partly matching page by copying its matching slots.  A request forked
-for parallel sampling shares every page; a shared, partly filled last page is copied before it is
-written (copy on write).  Behaviour follows tinyserve-llm's manager (kvcache/manager.py:127-321);
-what is new here are layer groups, window release, state slots and reservation in portions.
+Prefix reuse (where no group has a window and nothing needs per-request state).  What a request
+has committed goes on record, page by page, in the shared pool's `PrefixIndex`; the pages stay
+readable after the request has gone, until the pool needs them (`PagePool`: the page let go of
+longest ago that no other page continues from goes first).  A new request takes over the longest
+recorded start of its tokens: whole pages by reference, and of the next page the slots it begins
+with, by a copy.  A request forked for parallel sampling shares every page; whoever writes first
+into a shared, partly filled page gets a copy of its own (copy on write).  What is reused, when
+pages are shared, copied and given back follows tinyserve-llm's manager (kvcache/manager.py:127-321);
+the pools, the window release, state slots, reservation in portions, the admission plan and the
+index are this engine's own.
 
 Protocol per request: admit (reserve the first portion) -> step -> commit -> [extend -> step ->
 commit]* -> release.  Tables are valid from a reservation to the commit that follows it, and may
-change at commit (an identical page already cached replaces the request's own).
+change at commit (an identical page already on record replaces the request's own).
 """
 
 from __future__ import annotations
 
-from collections import OrderedDict
 from dataclasses import dataclass, field, replace
 from typing import Protocol, Sequence
 
-from tinyserve_llm_b200.cache.prefix_tree import PageNode, PrefixMatch, PrefixTree
+from tinyserve_llm_b200.cache.pool import CacheFull, PagePool
+from tinyserve_llm_b200.cache.prefix_index import CachedPage, PrefixIndex, Reuse
 
 
 @dataclass(frozen=True)
@@ -52,7 +55,8 @@ class CacheLayout:
 
     @property
     def prefix_reuse_possible(self) -> bool:
-        return len(self.groups) == 1 and self.groups[0].window == 0 and self.state_bytes == 0
+        """Cached pages can stand in for a prompt's start only if every layer keeps all keys and none keeps state."""
+        return bool(self.groups) and all(g.window == 0 for g in self.groups) and self.state_bytes == 0
 
     def group_of(self, entry: int) -> tuple[int, int]:
         """(group index, index of the entry inside its group)."""
@@ -110,7 +114,7 @@ PENDING_TOKEN = -1      # stands in the token record for a token that is still o
 
 @dataclass
 class SeqState:
-    tables: list[list[int]]                        # per group, page ids in token order (-1: given back)
+    tables: list[list[int]]                        # per pool, page ids in token order (-1: given back)
     tokens: list[int] = field(default_factory=list)  # one per reserved slot
     committed: int = 0
     state_slot: int = -1
@@ -122,7 +126,7 @@ class SeqState:
 
 @dataclass(frozen=True)
 class AdmissionCost:
-    pages_needed: tuple[int, ...]     # per group, to hold the whole request; compare with available_pages()
+    pages_needed: tuple[int, ...]     # per pool, to hold the whole request; compare with available_pages()
     prefill_tokens: int               # tokens the model has to run
 
 
@@ -140,21 +144,15 @@ class CacheStats:
     cached_pages: int = 0
 
 
-class CacheFull(RuntimeError):
-    """A reservation was asked for without checking that it fits."""
+@dataclass
+class _Admission:
+    """How a request would start: worked out once, priced by `admission_cost`, carried out by `admit`."""
 
-
-class _Pool:
-    """Reference counts and the free list of one group's pages."""
-
-    def __init__(self, num_pages: int) -> None:
-        self.num_pages = num_pages
-        self.refs = [0] * num_pages
-        self.free = list(range(num_pages - 1, -1, -1))     # pop() hands out page 0 first
-        self.free_cached: OrderedDict[int, None] = OrderedDict()   # ref 0 but still in the prefix tree, oldest first
-
-    def available(self) -> int:
-        return len(self.free) + len(self.free_cached)
+    reuse: Reuse                      # what the index offers
+    copy_from: CachedPage | None      # the page whose leading `reuse.run` slots are copied
+    reserve: int                      # tokens reserved right away, after the reused ones
+    demand: tuple[int, ...]           # pages each pool must have available (the largest need on the way, not the sum)
+    prefill_tokens: int
 
 
 class CacheManager:
@@ -165,12 +163,31 @@ class CacheManager:
         counts = [num_pages] * len(layout.groups) if isinstance(num_pages, int) else list(num_pages)
         if len(counts) != len(layout.groups) or any(c <= 0 for c in counts):
             raise ValueError(f"need a positive page count per layer group ({len(layout.groups)}), got {counts}")
-        self.pools = [_Pool(c) for c in counts]
         self.storage: Storage = storage if storage is not None else NullStorage()
         self.caching = bool(caching) and layout.prefix_reuse_possible
-        self.tree = PrefixTree(self.page_tokens)
+        # groups that keep all keys share the first pool made for one of them; a window group gets its own
+        self.pools: list[PagePool] = []
+        self.pool_of_group: list[int] = []
+        self.groups_of_pool: list[list[int]] = []
+        self.window_of_pool: list[int] = []
+        shared = -1
+        for g, (group, count) in enumerate(zip(layout.groups, counts)):
+            if group.window == 0 and shared >= 0:
+                self.pool_of_group.append(shared)
+                self.groups_of_pool[shared].append(g)
+                continue
+            if group.window == 0:
+                shared = len(self.pools)
+                count = min(c for c, other in zip(counts, layout.groups) if other.window == 0)
+            self.pool_of_group.append(len(self.pools))
+            self.groups_of_pool.append([g])
+            self.window_of_pool.append(group.window)
+            self.pools.append(PagePool(count))
+        self.shared = shared                               # index of the pool of the keep-all groups, -1 if there is none
+        self.index: PrefixIndex | None = None
+        if self.caching:
+            self.index = self.pools[shared].index = PrefixIndex(self.page_tokens)
         self.seqs: dict[int, SeqState] = {}
-        self._clock = 0
         self.counters = CacheStats()
         if layout.state_bytes and num_state_slots <= 0:
             raise ValueError("the model keeps per-request state: num_state_slots must be positive")
@@ -193,7 +210,7 @@ class CacheManager:
         return len(self._free_slots) if self.layout.state_bytes else 1 << 30
 
     def block_table(self, seq_id: int, group: int = 0) -> list[int]:
-        return self.seqs[seq_id].tables[group]
+        return self.seqs[seq_id].tables[self.pool_of_group[group]]
 
     def state_slot(self, seq_id: int) -> int:
         return self.seqs[seq_id].state_slot
@@ -206,171 +223,120 @@ class CacheManager:
         return self.seqs[seq_id].reserved
 
     def stats(self) -> CacheStats:
-        in_use = sum(p.num_pages - p.available() for p in self.pools)
-        return replace(self.counters, pages_in_use=in_use, cached_pages=len(self.tree.nodes))
+        return replace(self.counters, evictions=sum(p.evictions for p in self.pools),
+                       pages_in_use=sum(p.in_use() for p in self.pools),
+                       cached_pages=len(self.index) if self.index is not None else 0)
 
-    # ------------------------------------------------------------------ page bookkeeping
-    def _take(self, g: int) -> int:
-        pool = self.pools[g]
-        if pool.free:
-            page = pool.free.pop()
-        else:
-            page = self._evict(pool)
-        assert pool.refs[page] == 0
-        pool.refs[page] = 1
-        return page
-
-    def _evict(self, pool: _Pool) -> int:
-        # Oldest released first; a free page's descendants are free too and were released before
-        # it (tails go first), so the first leaf met is the least recently used one.
-        for page in pool.free_cached:
-            node = self.tree.nodes[page]
-            if not node.children:
-                del pool.free_cached[page]
-                self.counters.evictions += 1
-                return self.tree.evict(node)
-        raise CacheFull("no free page: check available_pages() before reserving")
-
-    def _hold(self, g: int, page: int) -> None:
-        pool = self.pools[g]
-        if pool.refs[page] == 0:
-            assert page in pool.free_cached, "a free page that is not cached must be taken, not held"
-            del pool.free_cached[page]
-        pool.refs[page] += 1
-
-    def _drop(self, g: int, page: int) -> None:
-        pool = self.pools[g]
-        assert pool.refs[page] > 0, f"page {page} of group {g} is released twice"
-        pool.refs[page] -= 1
-        if pool.refs[page]:
-            return
-        node = self.tree.nodes.get(page) if g == 0 else None
-        if node is None:
-            pool.free.append(page)
-        else:
-            self._clock += 1
-            node.stamp = self._clock
-            pool.free_cached[page] = None
+    def _copy(self, pool: int, src: int, dst: int, slots: int) -> None:
+        for g in self.groups_of_pool[pool]:                # the same page id in every group of the pool
+            self.storage.copy_slots(g, src, dst, slots)
 
     # ------------------------------------------------------------------ admission
-    def _source(self, match: PrefixMatch) -> PageNode | None:
-        """The page a partial match is copied from: one that is in use if there is one (it cannot be evicted)."""
-        if not match.partial_len:
-            return None
-        refs = self.pools[0].refs
-        return min(match.partial_sources, key=lambda p: (refs[p.page] == 0, p.page))
-
-    def _match(self, tokens: Sequence[int], reuse_limit: int | None = None) -> PrefixMatch:
-        if not self.caching:
-            return PrefixMatch([])
-        if reuse_limit is not None and reuse_limit < len(tokens) - 1:
-            tokens = tokens[:max(reuse_limit, 0) + 1]      # the walk stops one token short of what it is given
-        return self.tree.match(tokens)
-
-    def _cost(self, match: PrefixMatch, source: PageNode | None, num_tokens: int,
-              max_new: int | None = None) -> AdmissionCost:
+    def _plan(self, tokens: Sequence[int], max_new: int | None, reuse_limit: int | None) -> _Admission:
+        """
+        Read-only.  The demand on a pool is the most pages it has to give at any moment of the
+        admission and the request's later growth, counted as pages leaving `available()`:
+        an idle page that is taken over leaves it just as a blank page that is taken does.
+        """
         B = self.page_tokens
-        whole = -(-num_tokens // B)
-        first = num_tokens if max_new is None else min(num_tokens, match.num_tokens + max_new)
-        costs = []
-        for g, group in enumerate(self.layout.groups):
-            if g == 0 and self.caching:
-                refs = self.pools[0].refs
-                need = whole - len(match.pages)
-                last = match.pages[-1] if match.pages else None
-                if last is not None and len(last.tokens) < B and refs[last.page] > 0:
-                    need += 1                          # an attached, shared, partly filled page is copied on write
-                if source is not None and refs[source.page] == 0:
-                    need = max(need, 2)                # a free source must survive until its copy is made
-                need += sum(1 for p in match.pages if refs[p.page] == 0)   # attached free pages leave the pool
-                costs.append(need)
-            elif group.window:
-                costs.append(-(-first // B))           # a window group needs the first portion's pages only
+        total = len(tokens)
+        reuse = self.index.lookup(tokens, reuse_limit) if self.index is not None else Reuse([])
+        reserve = total - reuse.num_tokens if max_new is None else min(total - reuse.num_tokens, max_new)
+        whole_request = -(-total // B)
+        copy_from = None
+        demand = []
+        for p, pool in enumerate(self.pools):
+            if self.window_of_pool[p]:
+                demand.append(-(-(reuse.num_tokens + reserve) // B))     # later portions find pages the window has passed
+            elif self.index is None or p != self.shared:
+                demand.append(whole_request)
             else:
-                costs.append(whole)
-        return AdmissionCost(tuple(costs), num_tokens - match.num_tokens)
+                refs = pool.refs
+                if reuse.run:                              # a page in use cannot be evicted under the copy: prefer one
+                    copy_from = min(reuse.starting_with_run, key=lambda c: (refs[c.page] == 0, c.page))
+                woken = sum(1 for c in reuse.pages if refs[c.page] == 0)   # idle pages that come back into use
+                taken = whole_request - len(reuse.pages)    # blank pages over the request's life, the copy's target among them
+                last = reuse.pages[-1] if reuse.pages else None
+                if last is not None and not last.is_full(B) and refs[last.page] > 0:
+                    taken += 1                             # its holder writes there too: the request will write into a copy
+                if copy_from is not None and refs[copy_from.page] == 0:
+                    taken = max(taken, 2)                  # source and target exist side by side while the copy is made
+                demand.append(woken + taken)
+        return _Admission(reuse, copy_from, reserve, tuple(demand), total - reuse.num_tokens)
 
     def admission_cost(self, tokens: Sequence[int], max_new: int | None = None,
                        reuse_limit: int | None = None) -> AdmissionCost:
         """What admitting these tokens would take from the pools and how many tokens it would run.  Read-only."""
-        match = self._match(tokens, reuse_limit)
-        return self._cost(match, self._source(match), len(tokens), max_new)
+        plan = self._plan(tokens, max_new, reuse_limit)
+        return AdmissionCost(plan.demand, plan.prefill_tokens)
 
     def admit(self, seq_id: int, tokens: Sequence[int], max_new: int | None = None,
               reuse_limit: int | None = None) -> bool:
         """
-        Starts a request: attaches its cached prefix, copies a partial match, takes a state slot and
-        reserves slots for the next `max_new` tokens after the prefix (None: all the rest).  Returns
-        False, changing nothing, if the pools cannot hold the whole request right now.
-        `reuse_limit`: at most this many leading tokens are taken from the cache (a caller that
-        wants the model's output at a prompt position must have that position run).
+        Starts a request: takes over the recorded start of its tokens, copies the run a further
+        page begins with, takes a state slot and reserves slots for the next `max_new` tokens
+        (None: all the rest).  Returns False, changing nothing, if the pools cannot hold the whole
+        request right now.  `reuse_limit`: at most this many leading tokens are taken from the
+        cache (a caller that wants the model's output at a prompt position must have it run).
         """
         assert len(tokens) > 0, "a request needs at least one token"
         assert seq_id not in self.seqs, "the request is admitted already"
-        match = self._match(tokens, reuse_limit)
-        source = self._source(match)
-        if not self.fits(self._cost(match, source, len(tokens), max_new).pages_needed):
-            return False
-        if self.layout.state_bytes and not self._free_slots:
+        plan = self._plan(tokens, max_new, reuse_limit)
+        if not self.fits(plan.demand) or (self.layout.state_bytes and not self._free_slots):
             return False
         seq = SeqState(tables=[[] for _ in self.pools])
-        for node in match.pages:                       # hold matched pages before anything is taken: no eviction
-            self._hold(0, node.page)
-            seq.tables[0].append(node.page)
-        if source is not None:
-            self._hold(0, source.page)
-            dst = self._take(0)
-            self.storage.copy_slots(0, source.page, dst, match.partial_len)
-            self.counters.partial_copies += 1
-            self._drop(0, source.page)                 # the copy is ordered on the stream before any reuse
-            seq.tables[0].append(dst)
-        seq.committed = match.num_tokens
+        if plan.reuse.pages or plan.copy_from is not None:
+            pool, table = self.pools[self.shared], seq.tables[self.shared]
+            for cached in plan.reuse.pages:                # first all of them: a held page cannot be evicted below
+                pool.hold(cached.page)
+                table.append(cached.page)
+            if plan.copy_from is not None:
+                source = plan.copy_from.page
+                pool.hold(source)
+                target = pool.take()
+                self._copy(self.shared, source, target, plan.reuse.run)
+                pool.let_go(source)                        # the copy is ordered on the stream before any reuse of the page
+                table.append(target)
+                self.counters.partial_copies += 1
+        seq.committed = plan.reuse.num_tokens
         seq.tokens = list(tokens[:seq.committed])
         if self.layout.state_bytes:
             seq.state_slot = self._free_slots.pop()
             self.storage.clear_state(seq.state_slot)
-        rest = tokens[seq.committed:]
-        if max_new is not None:
-            rest = rest[:max_new]
         self.seqs[seq_id] = seq
-        self._reserve(seq, rest)
+        self._reserve(seq, tokens[seq.committed:seq.committed + plan.reserve])
         return True
 
     # ------------------------------------------------------------------ reservation
-    def _pages_to_reserve(self, seq: SeqState, n: int) -> tuple[int, ...]:
-        B = self.page_tokens
-        out = []
-        for g, pool in enumerate(self.pools):
-            table = seq.tables[g]
-            need = -(-(seq.reserved + n) // B) - len(table)
-            if seq.reserved % B and table and table[-1] >= 0 and pool.refs[table[-1]] > 1:
-                need += 1                              # the shared last page is copied before the write
-            out.append(max(need, 0))
-        return tuple(out)
+    def _shares_last_page(self, seq: SeqState, p: int) -> bool:
+        """The next token would land in a partly filled page that somebody else holds as well."""
+        table = seq.tables[p]
+        return bool(seq.reserved % self.page_tokens and table and table[-1] >= 0 and self.pools[p].refs[table[-1]] > 1)
+
+    def _growth(self, seq: SeqState, n: int) -> tuple[int, ...]:
+        """Pages each pool has to give for `n` more tokens of this request."""
+        pages_then = -(-(seq.reserved + n) // self.page_tokens)
+        return tuple(max(0, pages_then - len(seq.tables[p]) + self._shares_last_page(seq, p)) for p in range(len(self.pools)))
 
     def pages_needed_to_extend(self, seq_id: int, n: int) -> tuple[int, ...]:
-        return self._pages_to_reserve(self.seqs[seq_id], n)
+        return self._growth(self.seqs[seq_id], n)
 
     def can_extend(self, seq_id: int, n: int) -> bool:
-        return self.fits(self.pages_needed_to_extend(seq_id, n))
+        return self.fits(self._growth(self.seqs[seq_id], n))
 
     def pages_for_one_more_each(self, seq_ids: Sequence) -> list[int]:
-        """Per group, the pages that one more token for each of these requests would take: one pass, for large batches."""
+        """Per pool, the pages that one more token for each of these requests would take: one pass, for large batches."""
         B = self.page_tokens
-        need = [0] * len(self.pools)
-        seqs = self.seqs
+        total = [0] * len(self.pools)
         for seq_id in seq_ids:
-            seq = seqs[seq_id]
-            reserved = len(seq.tokens)
-            whole = reserved // B + 1
-            inside = reserved % B
-            for g, pool in enumerate(self.pools):
-                table = seq.tables[g]
-                if whole > len(table):
-                    need[g] += whole - len(table)
-                if inside and table and table[-1] >= 0 and pool.refs[table[-1]] > 1:
-                    need[g] += 1                       # the shared last page is copied before the write
-        return need
+            seq = self.seqs[seq_id]
+            fill = len(seq.tokens) % B
+            for p, table in enumerate(seq.tables):
+                if fill == 0:
+                    total[p] += 1                          # the token opens a page
+                elif table[-1] >= 0 and self.pools[p].refs[table[-1]] > 1:
+                    total[p] += 1                          # the token goes into a copy of the shared page
+        return total
 
     def extend(self, seq_id: int, tokens: Sequence[int], checked: bool = False) -> None:
         """
@@ -380,92 +346,89 @@ class CacheManager:
         assert len(tokens) > 0, "a step feeds at least one token"
         seq = self.seqs[seq_id]
         assert len(seq.tokens) == seq.committed, "the previous step was not committed"
-        if not checked and not self.fits(self._pages_to_reserve(seq, len(tokens))):
+        if not checked and not self.fits(self._growth(seq, len(tokens))):
             raise CacheFull("not enough free pages: check can_extend() first")
         self._reserve(seq, tokens)
 
     def _reserve(self, seq: SeqState, tokens: Sequence[int]) -> None:
         B = self.page_tokens
-        used = seq.reserved % B
-        for g, pool in enumerate(self.pools):
-            table = seq.tables[g]
-            if used and table and table[-1] >= 0:
-                last = table[-1]
-                if pool.refs[last] > 1:                # shared: copy on write
-                    fresh = self._take(g)
-                    self.storage.copy_slots(g, last, fresh, used)
-                    self.counters.cow_copies += 1
-                    self._drop(g, last)
-                    table[-1] = fresh
-                else:
-                    node = self.tree.nodes.get(last) if g == 0 else None
-                    assert node is None or used >= len(node.tokens), "a published slot would be overwritten"
-            want = -(-(seq.reserved + len(tokens)) // B)
-            while len(table) < want:
-                table.append(self._take(g))
+        fill = seq.reserved % B
+        pages_then = -(-(seq.reserved + len(tokens)) // B)
+        for p, pool in enumerate(self.pools):
+            table = seq.tables[p]
+            if self._shares_last_page(seq, p):             # copy on write
+                mine = pool.take()
+                self._copy(p, table[-1], mine, fill)
+                pool.let_go(table[-1])
+                table[-1] = mine
+                self.counters.cow_copies += 1
+            elif fill and table and table[-1] >= 0:
+                cached = pool.cached(table[-1])
+                assert cached is None or fill >= len(cached.tokens), "a slot on record would be overwritten"
+            table.extend(pool.take() for _ in range(pages_then - len(table)))
         seq.tokens.extend(tokens)
 
     # ------------------------------------------------------------------ commit / release / fork
     def commit(self, seq_id: int, num_accepted: int) -> None:
         """
         Closes a step: keeps the first `num_accepted` slots reserved since the last commit, drops the
-        rest, publishes pages that became full, and gives back pages a window has passed.
+        rest, puts pages that became full on record, and gives back pages a window has passed.
         """
         seq = self.seqs[seq_id]
-        assert 0 <= num_accepted <= seq.reserved - seq.committed, "more slots accepted than reserved"
-        assert not self.layout.state_bytes or num_accepted == seq.reserved - seq.committed, \
-            "a model with per-request state cannot take back tokens it has run"
+        fed = seq.reserved - seq.committed
+        assert 0 <= num_accepted <= fed, "more slots accepted than reserved"
+        assert not self.layout.state_bytes or num_accepted == fed, "a model with per-request state cannot take back tokens it has run"
         assert PENDING_TOKEN not in seq.tokens[seq.committed:seq.committed + num_accepted], \
             "a token still pending would be committed: amend it first"
         B = self.page_tokens
-        before = seq.committed
+        first_new_page = seq.committed // B
         seq.committed += num_accepted
         del seq.tokens[seq.committed:]
-        keep = -(-seq.committed // B)
-        for g in range(len(self.pools)):
-            table = seq.tables[g]
-            while len(table) > keep:
-                page = table.pop()
+        pages_kept = -(-seq.committed // B)
+        for p, pool in enumerate(self.pools):
+            table = seq.tables[p]
+            for page in table[pages_kept:]:                # pages only rejected tokens reached
                 if page >= 0:
-                    self._drop(g, page)
-        if self.caching:
-            for i in range(before // B, seq.committed // B):
-                self._publish(seq, i)
-        for g, group in enumerate(self.layout.groups):
-            if group.window:
-                self._release_behind_window(seq, g, group.window)
+                    pool.let_go(page)
+            del table[pages_kept:]
+            window = self.window_of_pool[p]
+            if window:
+                # the next query sits at position `committed` and sees keys from committed - window + 1 on
+                passed = min(max(0, seq.committed - window + 1) // B, len(table))
+                for i in range(passed):
+                    if table[i] >= 0:
+                        pool.let_go(table[i])
+                        table[i] = -1
+                        self.counters.window_releases += 1
+        if self.index is not None:
+            for i in range(first_new_page, seq.committed // B):
+                self._record(seq, i)
 
-    def _release_behind_window(self, seq: SeqState, g: int, window: int) -> None:
-        # The next query sits at position `committed` and sees keys >= committed - window + 1.
-        first_needed = max(0, seq.committed - window + 1)
-        table = seq.tables[g]
-        for i in range(min(first_needed // self.page_tokens, len(table))):
-            if table[i] >= 0:
-                self._drop(g, table[i])
-                table[i] = -1
-                self.counters.window_releases += 1
-
-    def _publish(self, seq: SeqState, i: int) -> None:
+    def _record(self, seq: SeqState, i: int) -> None:
+        """
+        Puts page `i` of the request on record with the committed tokens it holds.  If the index
+        knows a page with the same tokens at the same place, the request reads that one from now
+        on and gives its own back: two requests computed the same page, one copy is kept.
+        """
         B = self.page_tokens
-        table = seq.tables[0]
-        page = table[i]
-        parent = self.tree.nodes[table[i - 1]] if i else self.tree.root
-        tokens = seq.tokens[i * B:min((i + 1) * B, seq.committed)]
-        node = self.tree.nodes.get(page)
-        if node is None:
-            kept = self.tree.publish(parent, page, tokens)
-            if kept.page == page:
+        pool, table = self.pools[self.shared], seq.tables[self.shared]
+        mine = table[i]
+        held = tuple(seq.tokens[i * B:min((i + 1) * B, seq.committed)])
+        entry = self.index.by_page.get(mine)
+        if entry is None:
+            under = self.index.by_page[table[i - 1]] if i else self.index.root
+            kept = self.index.file(under, mine, held)
+            if kept.page == mine:
                 self.counters.publishes += 1
-        elif len(node.tokens) < len(tokens):
-            assert node.parent is parent
-            kept = self.tree.grow(node, tokens)
+        elif len(entry.tokens) < len(held):
+            kept = self.index.lengthen(entry, held)
         else:
             return
-        if kept.page != page:                          # the same tokens are cached already: use that page
-            self.counters.dedupes += 1
-            self._hold(0, kept.page)
+        if kept.page != mine:
+            pool.hold(kept.page)
             table[i] = kept.page
-            self._drop(0, page)
+            pool.let_go(mine)
+            self.counters.dedupes += 1
 
     def amend_last(self, seq_id: int, token: int) -> None:
         """Fills in the one reserved token that was extended as PENDING_TOKEN, before its commit."""
@@ -475,20 +438,23 @@ class CacheManager:
 
     def release(self, seq_id: int, drop_reserved: bool = False) -> None:
         """
-        Ends a request (finished or preempted).  With prefix reuse its pages stay cached until evicted.
-        `drop_reserved`: slots reserved for a step that will not be committed go with it (a request
-        that ended while its next step was already launched).
+        Ends a request (finished or preempted).  With prefix reuse everything it committed stays on
+        record, the partly filled last page too, until the pool needs the pages.  `drop_reserved`:
+        slots reserved for a step that will not be committed go with it (a request that ended
+        while its next step was already launched).
         """
         seq = self.seqs[seq_id]
         assert drop_reserved or seq.reserved == seq.committed, "release between steps: commit first"
         del seq.tokens[seq.committed:]
-        if self.caching and seq.committed % self.page_tokens:
-            self._publish(seq, seq.committed // self.page_tokens)
+        if self.index is not None and seq.committed % self.page_tokens:
+            self._record(seq, seq.committed // self.page_tokens)
         del self.seqs[seq_id]
-        for g in range(len(self.pools)):
-            for page in reversed(seq.tables[g]):       # tail first: leaves get older stamps than their parents
+        for pool, table in zip(self.pools, seq.tables):
+            # from the end: a page is let go of before the page it continues from, so of an idle chain the end
+            # is always the stalest part and goes first
+            for page in reversed(table):
                 if page >= 0:
-                    self._drop(g, page)
+                    pool.let_go(page)
         if seq.state_slot >= 0:
             self._free_slots.append(seq.state_slot)
 
@@ -506,9 +472,9 @@ class CacheManager:
                 raise CacheFull("no free state slot: check can_fork() first")
             slot = self._free_slots.pop()
             self.storage.copy_state(src.state_slot, slot)
-        for g in range(len(self.pools)):
-            for page in src.tables[g]:
+        for pool, table in zip(self.pools, src.tables):
+            for page in table:
                 if page >= 0:
-                    self._hold(g, page)
+                    pool.hold(page)
         self.seqs[new_id] = SeqState(tables=[list(t) for t in src.tables], tokens=list(src.tokens),
                                      committed=src.committed, state_slot=slot)

@@ -21,6 +21,7 @@ from __future__ import annotations
 
 import argparse
 import hashlib
+import itertools
 import json
 import math
 import random
@@ -31,19 +32,20 @@ from dataclasses import asdict, dataclass
 
 
 @dataclass
-class Turn:
-    user_ids: list[int]      # fed before this turn's reply: the first prompt, or the next user message
-    reply_len: int           # tokens to generate
-
-
-@dataclass
 class Conversation:
-    id: str
-    turns: list[Turn]
+    """One chat: the user's messages as token ids, and how many tokens each reply has."""
 
-    def history_len(self, k: int) -> int:
-        """Tokens in the conversation after turn k's reply (k counts from 1)."""
-        return sum(len(t.user_ids) + t.reply_len for t in self.turns[:k])
+    id: str
+    user_ids: list[list[int]]
+    reply_lens: list[int]
+
+    @property
+    def num_turns(self) -> int:
+        return len(self.reply_lens)
+
+    def lengths_after_turns(self) -> list[int]:
+        """Tokens in the conversation after each turn's reply."""
+        return list(itertools.accumulate(len(u) + r for u, r in zip(self.user_ids, self.reply_lens)))
 
 
 def synthetic_trace(n: int, vocab: int, max_model_len: int, seed: int, turns: tuple[int, int],
@@ -52,39 +54,71 @@ def synthetic_trace(n: int, vocab: int, max_model_len: int, seed: int, turns: tu
     rng = random.Random(seed)
     trace = []
     for c in range(n):
-        made, total = [], 0
+        messages, replies, total = [], [], 0
         for _ in range(rng.randint(*turns)):
             user, reply = rng.randint(*user_tokens), rng.randint(*reply_tokens)
             if total + user + reply > max_model_len:
                 break
-            made.append(Turn([rng.randrange(vocab) for _ in range(user)], reply))
+            messages.append([rng.randrange(vocab) for _ in range(user)])
+            replies.append(reply)
             total += user + reply
-        if made:
-            trace.append(Conversation(f"synthetic-{c}", made))
+        if replies:
+            trace.append(Conversation(f"synthetic-{c}", messages, replies))
     return trace
 
 
 def load_trace(path: str) -> tuple[dict, list[Conversation]]:
-    """{"meta": {...}, "conversations": [{"id", "turns": [{"user_ids", "reply_len"}]}]} (benchmarks/multiturn.py:150-155)."""
+    """
+    A trace file in tinyserve-llm's layout (benchmarks/multiturn.py:144-155):
+    {"meta": {...}, "conversations": [{"id": ..., "turns": [{"user_ids": [...], "reply_len": n}, ...]}, ...]}.
+    """
     with open(path) as f:
         raw = json.load(f)
-    return raw.get("meta", {}), [Conversation(c["id"], [Turn(t["user_ids"], t["reply_len"]) for t in c["turns"]])
-                                 for c in raw["conversations"]]
+    trace = []
+    for item in raw["conversations"]:
+        turns = item["turns"]
+        trace.append(Conversation(item["id"], [list(t["user_ids"]) for t in turns], [int(t["reply_len"]) for t in turns]))
+    return raw.get("meta", {}), trace
+
+
+def tokens_held_between_waves(trace: list[Conversation]) -> list[int]:
+    """
+    Entry k - 1: the tokens of all histories that are needed again after wave k, i.e. of the
+    conversations that have a turn k + 1.  One pass over the trace: each conversation adds its
+    length after every turn but its last.
+    """
+    held = [0] * max(0, max((c.num_turns for c in trace), default=0) - 1)
+    for conversation in trace:
+        for k, tokens in enumerate(conversation.lengths_after_turns()[:-1]):
+            held[k] += tokens
+    return held
 
 
 def peak_demand(trace: list[Conversation]) -> tuple[int, int]:
-    """(tokens, wave): after which wave the histories that still have a next turn hold the most tokens."""
-    best, best_k = 0, 0
-    for k in range(1, max(len(c.turns) for c in trace)):
-        tokens = sum(c.history_len(k) for c in trace if len(c.turns) > k)
-        if tokens > best:
-            best, best_k = tokens, k
-    return best, best_k
+    """
+    (tokens, wave): the most tokens the histories still needed hold between two waves, and after
+    which wave (0, 0 if no conversation has a second turn).  A cache of that many tokens serves
+    every next turn from its history; capacity over this is the pressure rho tinyserve-llm quotes
+    (benchmarks/multiturn.py:158-170).
+    """
+    held = tokens_held_between_waves(trace)
+    if not held:
+        return 0, 0
+    wave = max(range(len(held)), key=lambda k: (held[k], -k))
+    return held[wave], wave + 1
 
 
-def blocks_for(demand_tokens: int, rho: float, max_model_len: int, block_size: int) -> int:
-    """Pages for a target pressure, never fewer than one request of full length plus the scheduler's three spare pages."""
-    return max(math.ceil(demand_tokens / rho / block_size), math.ceil(max_model_len / block_size) + 3)
+def pool_pages(demand_tokens: int, rho: float, scheduler_config, block_size: int) -> int:
+    """
+    Pages for a target pressure, but never fewer than the scheduler wants before it takes a
+    request of `max_model_len` tokens at all (its own pages, one for the source of a copied page,
+    the watermark) and one to spare.
+    """
+    longest = -(-scheduler_config.max_model_len // block_size)
+    pages = longest + 2
+    while longest + 1 + math.ceil(scheduler_config.watermark * pages) > pages:
+        pages += 1
+    return max(math.ceil(demand_tokens / rho / block_size), pages + 1)
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -136,11 +170,11 @@ def main(argv: list[str] | None = None) -> int:
     if not trace:
         print("the trace holds no conversation that fits max_model_len", file=sys.stderr)
         return 2
-    demand, demand_wave = peak_demand(trace) if max(len(c.turns) for c in trace) > 1 else (0, 0)
-    num_blocks = None if args.rho == "full" else blocks_for(max(demand, 1), float(args.rho), max_model_len, args.block_size)
-
+    demand, demand_wave = peak_demand(trace)
     scheduler_config = SchedulerConfig(max_model_len=max_model_len, max_num_seqs=args.max_num_seqs,
                                        max_num_batched_tokens=args.max_num_batched_tokens)
+    num_blocks = None if args.rho == "full" else pool_pages(max(demand, 1), float(args.rho), scheduler_config, args.block_size)
+
     cache_config = CacheConfig(block_size=args.block_size, caching=args.caching == "on", device=args.device)
     llm = LLM(args.model, scheduler_config, cache_config, dtype=args.dtype, num_blocks=num_blocks,
               gpu_memory_utilization=args.gpu_memory_utilization, seed=args.seed, random_weights_seed=args.random_weights)
@@ -152,13 +186,13 @@ def main(argv: list[str] | None = None) -> int:
     llm.generate([[7] * min(17, max_model_len - 4)], SamplingParams(max_tokens=4, temperature=0.0, ignore_eos=True))
 
     history: list[list[int]] = [[] for _ in trace]
-    waves = max(len(c.turns) for c in trace)
+    waves = max(c.num_turns for c in trace)
     records = []
     started = time.time()
     for k in range(waves if args.max_waves is None else min(waves, args.max_waves)):
-        live = [i for i, c in enumerate(trace) if len(c.turns) > k]
-        prompts = [history[i] + trace[i].turns[k].user_ids for i in live]
-        lengths = [trace[i].turns[k].reply_len for i in live]
+        live = [i for i, c in enumerate(trace) if c.num_turns > k]
+        prompts = [history[i] + trace[i].user_ids[k] for i in live]
+        lengths = [trace[i].reply_lens[k] for i in live]
         before = llm.scheduler.stats()
         begin = time.perf_counter()
         done = llm.generate(prompts, [SamplingParams(max_tokens=n, temperature=args.temperature, ignore_eos=True)

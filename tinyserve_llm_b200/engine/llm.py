@@ -18,7 +18,7 @@ from dataclasses import dataclass, replace
 
 import torch
 
-from tinyserve_llm_b200.cache.manager import CacheStats, plan_layout
+from tinyserve_llm_b200.cache.manager import PENDING_TOKEN, CacheStats, plan_layout
 from tinyserve_llm_b200.cache.storage import DeviceCacheStorage
 from tinyserve_llm_b200.engine.loading import build_cache, load_model, require_cuda, resolve_dtype
 from tinyserve_llm_b200.engine.scheduler import RequestOutput, ScheduledSeq, Scheduler, SchedulerConfig, SchedulerStats
@@ -231,18 +231,19 @@ class LLM:
     def _launch(self, batch: list[ScheduledSeq], before: "_InFlight | None" = None) -> "_InFlight":
         """
         Queues the step and its sampling on the device; nothing waits.  With `before` (the step
-        under way, whose samples the host has not seen) every entry's token is that step's sample
-        for the same sequence, passed on the device, and its output position is one further on.
+        under way, whose samples the host has not seen) an entry that feeds the unknown token gets
+        that step's sample for the same sequence, passed on the device, and its output position is
+        one further on; entries that feed a prompt portion are as ever.
         """
         entries, temperatures, draws, rows = [], [], [], []
         first_draw: dict[int, int] = {}
         row = 0
-        lag = 0 if before is None else 1
         for seq, fed, num_samples in batch:
-            if before is None:
-                entries.append(StepEntry(seq.seq_id, fed, [len(fed) - 1] if num_samples else []))
+            lag = 1 if (before is not None and fed[0] == PENDING_TOKEN) else 0
+            if lag:
+                entries.append(StepEntry(seq.seq_id, (0,), (0,) if num_samples else (), feed=before.first_draw[seq.seq_id]))
             else:
-                entries.append(StepEntry(seq.seq_id, (0,), (0,), feed=before.first_draw[seq.seq_id]))
+                entries.append(StepEntry(seq.seq_id, fed, [len(fed) - 1] if num_samples else []))
             first_draw[seq.seq_id] = len(draws)
             for i in range(num_samples):
                 index = seq.sample_index if num_samples == 1 else i

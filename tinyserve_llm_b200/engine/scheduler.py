@@ -20,14 +20,21 @@ run again from its whole token list.  A prompt portion that finds no page waits 
 If a step would otherwise be empty while sequences are running, the lowest-scoring one is preempted
 and the step is built again; a step that is empty with nothing running raises in the engine.
 
-Running ahead (new here).  While a decode step is still on the device, `schedule_ahead` may decide
-the step after it: every running sequence feeds the token it is about to sample, which the engine
-passes from step to step on the device.  It does so only where the decision does not depend on
-those tokens: nothing waits (or nothing waiting could be admitted: the sequence cap is full, or the last
-admission pass found room for none and nothing has made room since), everything running is in the step
-and samples one token, and the pages for one more token each are free.  A sequence that reaches `max_tokens` in the step under way is
-left out.  The one thing unknown is an end-of-sequence token: a sequence that samples one finishes
-as usual, its pages are released, and its share of the step launched ahead is thrown away.
+Running ahead (new here).  While a step is still on the device, `schedule_ahead` may decide the
+step after it: a sequence that samples in the step under way feeds the token it is about to
+sample, which the engine passes from step to step on the device, and a sequence still in its
+prompt feeds its next portion.  It does so only where the decision does not depend on the samples:
+nothing waits (or nothing waiting could be admitted: the sequence cap is full, or the last
+admission pass found room for none and nothing has made room since), everything running is in the
+step, no group forks, and the pages the next step takes are free.  A sequence that reaches
+`max_tokens` in the step under way is left out.  The one thing unknown is an end-of-sequence token:
+a sequence that samples one finishes as usual, its pages are released, and its share of the step
+launched ahead is thrown away.
+
+The policy (what is ranked how, who gives way, what an admission must leave free) is
+tinyserve-llm's; how a step is put together here is this engine's own: a draft that is filled by
+decodes, prompt portions and admissions in turn, room for decodes made by one count over the
+whole batch, and admission conditions kept as the seats, pages and state slots that are left.
 """
 
 from __future__ import annotations
@@ -93,6 +100,28 @@ class RequestOutput(NamedTuple):
     sequences: list[Sequence]
 
 
+class _Draft:
+    """A step being put together: what is in it, and what is left of the token budget."""
+
+    def __init__(self, tokens_left: int) -> None:
+        self.entries: list[ScheduledSeq] = []
+        self.tokens_left = tokens_left
+
+    def add(self, seq: Sequence, tokens: list[int], num_samples: int) -> None:
+        self.entries.append(ScheduledSeq(seq, tokens, num_samples))
+        self.tokens_left -= len(tokens)
+
+
+class Candidate(NamedTuple):
+    """A waiting sequence as an admission pass sees it."""
+
+    seq: Sequence
+    tokens: list[int]             # prompt and, after a preemption, the outputs so far
+    cost: AdmissionCost
+    hit: float
+    priority: float
+
+
 class Scheduler:
     def __init__(self, config: SchedulerConfig, cache: CacheManager) -> None:
         self.config = config
@@ -113,7 +142,23 @@ class Scheduler:
     def has_unfinished(self) -> bool:
         return bool(self.waiting or self.running)
 
+    def stats(self) -> SchedulerStats:
+        return replace(self.counters, num_waiting=len(self.waiting), num_running=len(self.running))
+
     # ------------------------------------------------------------------ intake
+    def _never_fits(self, length: int, params: SamplingParams) -> str | None:
+        """Why a request of `length` tokens at its longest could not run even with the engine to itself."""
+        if length > self.config.max_model_len:
+            return f"prompt + max_tokens = {length} exceeds max_model_len = {self.config.max_model_len}"
+        # at its longest: its own pages, one copied page per further sample, what admissions must leave free, and the
+        # page that holds a partly matching cached page while its slots are copied
+        pages = -(-length // self.cache.page_tokens) + (params.n - 1) + self.watermark_pages + 1
+        if pages > self.cache.num_pages:
+            return f"needs up to {pages} pages; the cache has {self.cache.num_pages}"
+        if params.n > self.config.max_num_seqs:
+            return f"n = {params.n} samples exceed max_num_seqs = {self.config.max_num_seqs}"
+        return None
+
     def add_request(self, prompt_token_ids: list[int], params: SamplingParams, arrival_time: float) -> int:
         """Queues a request and returns its id; rejects one that could never run."""
         if not prompt_token_ids:
@@ -122,16 +167,9 @@ class Scheduler:
             raise ValueError("max_tokens and n must be at least 1")
         if params.temperature < 0:
             raise ValueError("temperature must not be negative")
-        longest = len(prompt_token_ids) + params.max_tokens
-        if longest > self.config.max_model_len:
-            raise ValueError(f"prompt + max_tokens = {longest} exceeds max_model_len = {self.config.max_model_len}")
-        # one sequence at full length, a copied page per fork, the watermark, and one page that
-        # holds a partly matching cached page while its slots are copied
-        worst = -(-longest // self.cache.page_tokens) + (params.n - 1) + self.watermark_pages + 1
-        if worst > self.cache.num_pages:
-            raise ValueError(f"needs up to {worst} pages; the cache has {self.cache.num_pages}")
-        if params.n > self.config.max_num_seqs:
-            raise ValueError(f"n = {params.n} samples exceed max_num_seqs = {self.config.max_num_seqs}")
+        problem = self._never_fits(len(prompt_token_ids) + params.max_tokens, params)
+        if problem is not None:
+            raise ValueError(problem)
         request_id = next(self._request_ids)
         seq = Sequence(next(self._seq_ids), request_id, tuple(prompt_token_ids), params, arrival_time)
         self.groups[request_id] = [seq]
@@ -139,147 +177,146 @@ class Scheduler:
         self._nothing_admissible = False
         return request_id
 
-    # ------------------------------------------------------------------ ranking
-    def _hit(self, num_tokens: int, cost: AdmissionCost) -> float:
-        cached = num_tokens - cost.prefill_tokens
-        return cached / (self.config.max_model_len if self.config.hit_mode == "absolute" else num_tokens)
+    # ------------------------------------------------------------------ priority
+    def priority(self, seq: Sequence, now: float, hit: float | None = None) -> float:
+        """
+        Cache hit plus weighted wait (scheduler/scheduler.py:89-117 of tinyserve-llm): a waiting
+        sequence is ranked by the hit it would have now, a running one keeps the hit it was admitted
+        with, and both keep ageing from their arrival.
+        """
+        return (seq.admission_hit if hit is None else hit) + self.config.wait_weight * (now - seq.arrival_time)
 
-    def _score(self, hit: float, seq: Sequence, now: float) -> float:
-        return hit + self.config.wait_weight * (now - seq.arrival_time)
+    def _candidate(self, seq: Sequence, now: float) -> Candidate:
+        tokens = seq.all_token_ids
+        cost = self.cache.admission_cost(tokens)
+        scale = self.config.max_model_len if self.config.hit_mode == "absolute" else len(tokens)
+        hit = (len(tokens) - cost.prefill_tokens) / scale
+        return Candidate(seq, tokens, cost, hit, self.priority(seq, now, hit))
 
-    def _ranked_waiting(self, now: float) -> list[tuple[Sequence, AdmissionCost, float]]:
-        ranked = []
-        for order, seq in enumerate(self.waiting):
-            tokens = seq.all_token_ids
-            cost = self.cache.admission_cost(tokens)
-            hit = self._hit(len(tokens), cost)
-            ranked.append((-self._score(hit, seq, now), order, seq, cost, hit))
-        ranked.sort(key=lambda r: (r[0], r[1]))
-        return [(seq, cost, hit) for _, _, seq, cost, hit in ranked]
+    def waiting_by_rank(self, now: float) -> list[Candidate]:
+        """The waiting sequences, best first; earlier arrival breaks a tie."""
+        candidates = [self._candidate(seq, now) for seq in self.waiting]
+        order = sorted(range(len(candidates)), key=lambda i: (-candidates[i].priority, i))
+        return [candidates[i] for i in order]
 
-    def _portion(self, remaining: int, budget: int) -> int:
-        n = min(remaining, budget)
-        if self.config.prefill_chunk:
-            n = min(n, self.config.prefill_chunk)
-        return n
+    def _lowest(self, seqs: list[Sequence], now: float) -> Sequence:
+        return min(seqs, key=lambda s: self.priority(s, now))
 
-    # ------------------------------------------------------------------ building a step
-    def schedule(self, now: float) -> list[ScheduledSeq]:
-        while True:
-            batch = self._build(now)
-            if batch or not self.running:
-                return batch
-            # everything running is stalled for pages: free the lowest-scoring one and try again
-            victim = min(self.running, key=lambda s: self._score(s.admission_hit, s, now))
-            self.running.remove(victim)
-            self._preempt(victim)
-
-    def _build(self, now: float) -> list[ScheduledSeq]:
-        budget = self.config.max_num_batched_tokens
-        if self.config.step_mode == "prefill_first":
-            first = self._continue_prefills(now, budget)
-            budget -= sum(len(s.token_ids) for s in first)
-            first += self._admit(now, budget)
-            return first or self._schedule_decodes(now)
-        decodes = self._schedule_decodes(now)
-        budget -= len(decodes)
-        portions = self._continue_prefills(now, budget)
-        budget -= sum(len(s.token_ids) for s in portions)
-        return decodes + portions + self._admit(now, budget)
-
-    def _remaining(self, seq: Sequence) -> int:
+    # ------------------------------------------------------------------ what a sequence does next
+    def _left_to_run(self, seq: Sequence) -> int:
         return seq.num_tokens - self.cache.committed_tokens(seq.seq_id)
 
-    def _is_decoding(self, seq: Sequence) -> bool:
-        return bool(seq.output_token_ids) and self._remaining(seq) == 1
+    def _decoding(self, seq: Sequence) -> bool:
+        return bool(seq.output_token_ids) and self._left_to_run(seq) == 1
 
-    def _schedule_decodes(self, now: float) -> list[ScheduledSeq]:
-        decoding = [s for s in self.running if self._is_decoding(s)]
-        others = [s for s in self.running if not self._is_decoding(s)]
-        queue = sorted(decoding, key=lambda s: self._score(s.admission_hit, s, now))    # lowest score first
-        scheduled: list[ScheduledSeq] = []
-        kept: list[Sequence] = []
-        while queue:
-            seq = queue.pop()                                    # highest score left
-            while not self.cache.can_extend(seq.seq_id, 1) and queue:
-                self._preempt(queue.pop(0))
-            if not self.cache.can_extend(seq.seq_id, 1):
-                # nothing decoding ranks lower; a sequence still in its prompt may give way instead
-                victim = min(others, key=lambda s: self._score(s.admission_hit, s, now), default=None)
-                if victim is not None and self._score(victim.admission_hit, victim, now) < \
-                        self._score(seq.admission_hit, seq, now):
-                    others.remove(victim)
-                    self._preempt(victim)
-                if not self.cache.can_extend(seq.seq_id, 1):
-                    self._preempt(seq)
-                    break
-            token = seq.output_token_ids[-1]
-            self.cache.extend(seq.seq_id, [token])
-            scheduled.append(ScheduledSeq(seq, [token], 1))
-            self.counters.decode_tokens += 1
-            kept.append(seq)
-        self.running = kept + queue + others
-        return scheduled
+    def _portion(self, left_to_run: int, tokens_left: int) -> int:
+        n = min(left_to_run, tokens_left)
+        return min(n, self.config.prefill_chunk) if self.config.prefill_chunk else n
 
-    def _continue_prefills(self, now: float, budget: int) -> list[ScheduledSeq]:
-        out: list[ScheduledSeq] = []
-        pending = [s for s in self.running if not self._is_decoding(s) and self.cache.reserved_tokens(s.seq_id)
-                   == self.cache.committed_tokens(s.seq_id)]
-        pending.sort(key=lambda s: -self._score(s.admission_hit, s, now))
-        for seq in pending:
-            if budget <= 0:
-                break
-            remaining = self._remaining(seq)
-            n = self._portion(remaining, budget)
-            if not self.cache.can_extend(seq.seq_id, n):
-                self.counters.stalled_portions += 1
-                continue
-            start = seq.num_tokens - remaining
-            tokens = seq.all_token_ids[start:start + n]
-            self.cache.extend(seq.seq_id, tokens)
-            self.counters.prefill_tokens += n
-            budget -= n
-            out.append(ScheduledSeq(seq, tokens, self._samples_after(seq, n == remaining)))
-        return out
-
-    def _samples_after(self, seq: Sequence, reaches_end: bool) -> int:
+    @staticmethod
+    def _samples_after(seq: Sequence, reaches_end: bool) -> int:
+        """How many tokens are drawn after a step: none inside a prompt, n where a group's prompt ends, else one."""
         if not reaches_end:
             return 0
         return seq.params.n if (seq.params.n > 1 and not seq.output_token_ids) else 1
 
+    # ------------------------------------------------------------------ putting a step together
+    def schedule(self, now: float) -> list[ScheduledSeq]:
+        while True:
+            draft = self._draft(now)
+            if draft.entries or not self.running:
+                return draft.entries
+            self._preempt(self._lowest(self.running, now))      # everything running waits for pages: one gives way
+
+    def _draft(self, now: float) -> _Draft:
+        draft = _Draft(self.config.max_num_batched_tokens)
+        if self.config.step_mode == "prefill_first":
+            self._add_portions(draft, now)
+            self._add_admissions(draft, now)
+            if not draft.entries:
+                self._add_decodes(draft, now)
+        else:
+            self._add_decodes(draft, now)
+            self._add_portions(draft, now)
+            self._add_admissions(draft, now)
+        return draft
+
+    def _add_decodes(self, draft: _Draft, now: float) -> None:
+        """
+        Every decoding sequence feeds its last token.  If the pages their next tokens need are not all
+        there (counted in one pass over the batch), the lowest-ranked running sequence gives way, decoding
+        or still in its prompt, until they are; decodes may use what admissions have to leave free.
+        """
+        decoding = [s for s in self.running if self._decoding(s)]
+        while decoding and not self.cache.fits(self.cache.pages_for_one_more_each([s.seq_id for s in decoding])):
+            victim = self._lowest(self.running, now)
+            self._preempt(victim)
+            if victim in decoding:
+                decoding.remove(victim)
+        decoding.sort(key=lambda s: -self.priority(s, now))
+        for seq in decoding:
+            token = seq.output_token_ids[-1]
+            self.cache.extend(seq.seq_id, [token], checked=True)
+            draft.add(seq, [token], 1)
+        self.counters.decode_tokens += len(decoding)
+
+    def _add_portions(self, draft: _Draft, now: float) -> None:
+        """Sequences still in their prompt (or recomputing after a preemption) feed their next portion, best first."""
+        in_prompt = [s for s in self.running if not self._decoding(s)
+                     and self.cache.reserved_tokens(s.seq_id) == self.cache.committed_tokens(s.seq_id)]
+        in_prompt.sort(key=lambda s: -self.priority(s, now))
+        for seq in in_prompt:
+            if draft.tokens_left <= 0:
+                break
+            left = self._left_to_run(seq)
+            n = self._portion(left, draft.tokens_left)
+            if not self.cache.can_extend(seq.seq_id, n):
+                self.counters.stalled_portions += 1              # waits for pages; a later step takes it up
+                continue
+            begin = seq.num_tokens - left
+            tokens = seq.all_token_ids[begin:begin + n]
+            self.cache.extend(seq.seq_id, tokens)
+            self.counters.prefill_tokens += n
+            draft.add(seq, tokens, self._samples_after(seq, n == left))
+
     def _preempt(self, seq: Sequence) -> None:
-        self._nothing_admissible = False
+        """The sequence gives its pages back (they stay cached) and waits again, with its outputs and its arrival time."""
+        self.running.remove(seq)
         self.cache.release(seq.seq_id)
         seq.status = SequenceStatus.WAITING
         seq.num_preemptions += 1
         self.counters.preemptions += 1
         self.waiting.append(seq)
+        self._nothing_admissible = False
 
-    def _admit(self, now: float, budget: int) -> list[ScheduledSeq]:
-        admitted: list[ScheduledSeq] = []
-        evaluated = budget > 0 and bool(self.waiting)
-        owed_forks = 0                                   # forks of groups admitted earlier in this step
-        for seq, cost, hit in self._ranked_waiting(now):
-            if budget <= 0:
+    def _add_admissions(self, draft: _Draft, now: float) -> None:
+        """
+        Waiting sequences in rank order, while the draft has tokens left.  One is admitted if a seat, the
+        pages and a state slot are there for it and for the further samples its group will fork into, with
+        the watermark left free; a misfit is passed over while young, and ends the pass once it has waited
+        `max_skip_wait`, so that what comes free goes to it (scheduler/scheduler.py:160-204 of tinyserve-llm).
+        """
+        considered = draft.tokens_left > 0 and bool(self.waiting)
+        seats = self.config.max_num_seqs - len(self.running)
+        forks_owed = 0                       # further samples of groups admitted in this pass: each takes a page and a slot later
+        admitted: list[Sequence] = []
+        for candidate in self.waiting_by_rank(now):
+            if draft.tokens_left <= 0:
                 break
-            tokens = seq.all_token_ids
-            if admitted:                                 # an earlier admission may have evicted what this hit counted on
-                cost = self.cache.admission_cost(tokens)
-                hit = self._hit(len(tokens), cost)
-            first_of_group = seq.params.n > 1 and not seq.output_token_ids
-            forks = seq.params.n - 1 if first_of_group else 0
-            n = self._portion(cost.prefill_tokens, budget)
-            fits = (
-                len(self.running) + owed_forks + 1 + forks <= self.config.max_num_seqs
-                and self.cache.fits(cost.pages_needed, owed_forks + forks + self.watermark_pages)
-                and self.cache.free_state_slots() >= 1 + owed_forks + forks
-            )
-            if not fits:
+            if admitted:                     # an admission may have evicted what this one's hit counted on
+                candidate = self._candidate(candidate.seq, now)
+            seq, tokens, cost = candidate.seq, candidate.tokens, candidate.cost
+            branches = seq.params.n - 1 if (seq.params.n > 1 and not seq.output_token_ids) else 0
+            room = (seats >= 1 + branches
+                    and self.cache.fits(cost.pages_needed, forks_owed + branches + self.watermark_pages)
+                    and self.cache.free_state_slots() >= 1 + forks_owed + branches)
+            if not room:
                 if now - seq.arrival_time >= self.config.max_skip_wait:
                     break
                 continue
-            ok = self.cache.admit(seq.seq_id, tokens, n)
-            assert ok, "the fit check used a fresh cost"
+            n = self._portion(cost.prefill_tokens, draft.tokens_left)
+            started = self.cache.admit(seq.seq_id, tokens, n)
+            assert started, "the room was checked against a fresh cost"
             cached = self.cache.committed_tokens(seq.seq_id)
             fed = tokens[cached:cached + n]
             if seq.num_preemptions:
@@ -288,58 +325,84 @@ class Scheduler:
                 self.counters.admissions += 1
             self.counters.cached_tokens += cached
             self.counters.prefill_tokens += len(fed)
-            budget -= len(fed)
-            owed_forks += forks
+            seats -= 1 + branches
+            forks_owed += branches
             seq.status = SequenceStatus.RUNNING
-            seq.admission_hit = hit
+            seq.admission_hit = candidate.hit
             self.running.append(seq)
-            admitted.append(ScheduledSeq(seq, fed, self._samples_after(seq, cached + len(fed) == len(tokens))))
+            admitted.append(seq)
+            draft.add(seq, fed, self._samples_after(seq, cached + len(fed) == len(tokens)))
         if admitted:
-            chosen = {s.seq.seq_id for s in admitted}
-            self.waiting = [s for s in self.waiting if s.seq_id not in chosen]
-        self._nothing_admissible = evaluated and not admitted
+            gone = {s.seq_id for s in admitted}
+            self.waiting = [s for s in self.waiting if s.seq_id not in gone]
+        self._nothing_admissible = considered and not admitted
         self._window_releases_seen = self.cache.counters.window_releases
-        return admitted
 
     # ------------------------------------------------------------------ the step after the one under way
     def schedule_ahead(self, under_way: list[ScheduledSeq]) -> list[ScheduledSeq] | None:
         """
         The step that follows `under_way`, whose samples are not known yet; None where that step
         depends on them (then nothing is changed).  Otherwise `under_way` is committed here (its
-        tokens are known, and whatever reads their keys is launched after it), each continuing
-        sequence reserves one slot with PENDING_TOKEN as its token, and `postprocess` is told so.
+        tokens are known, and whatever reads their keys is launched after it), each sequence that
+        samples in it reserves one slot with PENDING_TOKEN as its token, each sequence still in
+        its prompt its next portion, and `postprocess` is told so.
         """
-        alive = [s for s in under_way if s.seq.status is SequenceStatus.RUNNING]
-        if any(s.num_samples != 1 for s in alive) or {s.seq.seq_id for s in alive} != {s.seq_id for s in self.running}:
+        alive = [e for e in under_way if e.seq.status is SequenceStatus.RUNNING]
+        if any(e.num_samples > 1 for e in alive):
+            return None                          # a group forks once its samples are known
+        if {e.seq.seq_id for e in alive} != {s.seq_id for s in self.running}:
+            return None                          # somebody running sat the step out: a full pass decides what is next
+        # the step under way gives a sampling sequence output number len(outputs) + 1
+        samplers = [e.seq for e in alive if e.num_samples and len(e.seq.output_token_ids) + 1 < e.seq.params.max_tokens]
+        in_prompt = [e.seq for e in alive if not e.num_samples]
+        ending = len(alive) - len(samplers) - len(in_prompt)
+        if not samplers and not in_prompt:
             return None
-        # the step under way produces output number len(outputs) + 1
-        going_on = [s.seq for s in alive if len(s.seq.output_token_ids) + 1 < s.seq.params.max_tokens]
-        if not going_on:
-            return None
+        if in_prompt and self.config.step_mode == "prefill_first":
+            return None                          # such a step holds the prompts alone; the sequences that sample sit it out
         # Requests that wait rule the step out unless none of them could be admitted into it anyway: nobody
         # reaches max_tokens in the step under way, and either the sequence cap is full or the last admission
         # pass found room for none of them and nothing has made room since.  A request that ends on an
         # end-of-sequence token then hands its place on one step later than it would have.
         if self.waiting:
-            if len(going_on) < len(alive):
+            if ending:
                 return None
-            blocked = self._nothing_admissible and self._window_releases_seen == self.cache.counters.window_releases
-            if not blocked and len(self.running) < self.config.max_num_seqs:
+            stuck = self._nothing_admissible and self._window_releases_seen == self.cache.counters.window_releases
+            if not stuck and len(self.running) < self.config.max_num_seqs:
                 return None
-        if not self.cache.fits(self.cache.pages_for_one_more_each([seq.seq_id for seq in going_on])):
-            return None                          # someone has to give way: decided when the tokens are known
-        for s in alive:
-            self.cache.commit(s.seq.seq_id, len(s.token_ids))
-        pending = [PENDING_TOKEN]
-        ahead = []
-        for seq in going_on:
-            self.cache.extend(seq.seq_id, pending, checked=True)
-            ahead.append(ScheduledSeq(seq, pending, 1))
-        self.counters.decode_tokens += len(ahead)
-        return ahead
+        # the pages of the whole step, or nothing: who gives way is decided when the tokens are known
+        tokens_left = self.config.max_num_batched_tokens - len(samplers)
+        portions: list[tuple[Sequence, int, int]] = []
+        need = self.cache.pages_for_one_more_each([s.seq_id for s in samplers])
+        for seq in sorted(in_prompt, key=lambda s: -self.priority(s, 0.0)):
+            left = seq.num_tokens - self.cache.reserved_tokens(seq.seq_id)     # what is reserved is under way
+            n = self._portion(left, tokens_left)
+            if n <= 0:
+                return None
+            need = [a + b for a, b in zip(need, self.cache.pages_needed_to_extend(seq.seq_id, n))]
+            portions.append((seq, left, n))
+            tokens_left -= n
+        if not self.cache.fits(need):
+            return None
+        for e in alive:
+            self.cache.commit(e.seq.seq_id, len(e.token_ids))
+        ahead = _Draft(self.config.max_num_batched_tokens)
+        unknown = [PENDING_TOKEN]
+        for seq in samplers:
+            self.cache.extend(seq.seq_id, unknown, checked=True)
+            ahead.add(seq, unknown, 1)
+        self.counters.decode_tokens += len(samplers)
+        for seq, left, n in portions:
+            begin = seq.num_tokens - left
+            tokens = seq.all_token_ids[begin:begin + n]
+            self.cache.extend(seq.seq_id, tokens, checked=True)
+            self.counters.prefill_tokens += n
+            ahead.add(seq, tokens, self._samples_after(seq, n == left))
+        return ahead.entries
 
     # ------------------------------------------------------------------ after the model ran
-    def _fork(self, parent: Sequence, index: int) -> Sequence:
+    def _branch(self, parent: Sequence, index: int) -> Sequence:
+        """A further sample of a group: a sequence of its own that shares every page of the prompt."""
         child = Sequence(next(self._seq_ids), parent.request_id, parent.prompt_token_ids, parent.params,
                          parent.arrival_time, status=SequenceStatus.RUNNING, sample_index=index,
                          admission_hit=parent.admission_hit)
@@ -348,55 +411,52 @@ class Scheduler:
         self.groups[parent.request_id].append(child)
         return child
 
-    def _finish_reason(self, seq: Sequence, token: int) -> str | None:
+    def _deliver(self, seq: Sequence, token: int, now: float, reserved_ahead: bool) -> bool:
+        """Books one sampled token; True if the sequence ends with it (an end-of-sequence token is kept)."""
+        seq.output_token_ids.append(token)
+        if seq.first_token_time is None:
+            seq.first_token_time = now
         if token == self.config.eos_token_id and not seq.params.ignore_eos:
-            return "eos"
-        if len(seq.output_token_ids) >= seq.params.max_tokens:
-            return "length"
-        return None
+            seq.finish_reason = "eos"
+        elif len(seq.output_token_ids) >= seq.params.max_tokens:
+            seq.finish_reason = "length"
+        else:
+            return False
+        self.cache.release(seq.seq_id, drop_reserved=reserved_ahead)
+        seq.status = SequenceStatus.FINISHED
+        seq.finish_time = now
+        return True
 
     def postprocess(self, scheduled: list[ScheduledSeq], sampled: list[list[int]], now: float,
                     ahead: list[ScheduledSeq] | None = None) -> list[RequestOutput]:
         """
-        Commits the step, forks groups after their first sampling step, records tokens, frees what
+        Closes the step, lets groups fork where their prompt ended, books the tokens and frees what
         finished.  `ahead` is what `schedule_ahead(scheduled)` returned: the step is committed
-        already, and the sequences in `ahead` get their pending token filled in.  Samples of a
-        sequence that finished while this step was launched ahead are dropped.
+        already, and the sequences that feed an unknown token in `ahead` get it filled in.  Samples
+        of a sequence that finished while this step was launched ahead are dropped.
         """
-        finished: list[Sequence] = []
-        pending = {s.seq.seq_id for s in ahead} if ahead is not None else ()
+        in_ahead = {e.seq.seq_id for e in ahead} if ahead is not None else set()
+        fed_unknown = {e.seq.seq_id for e in ahead if e.token_ids[0] == PENDING_TOKEN} if ahead is not None else set()
+        ended: list[Sequence] = []
         for (seq, token_ids, num_samples), tokens in zip(scheduled, sampled, strict=True):
             assert len(tokens) == num_samples
             if seq.status is SequenceStatus.FINISHED:
                 continue
             if ahead is None:
                 self.cache.commit(seq.seq_id, len(token_ids))
-            elif seq.seq_id in pending:
+            elif seq.seq_id in fed_unknown:
                 self.cache.amend_last(seq.seq_id, tokens[0])
-            if num_samples == 0:
-                continue
-            samples = [seq] + [self._fork(seq, i) for i in range(1, num_samples)]
+            samples = [seq] + [self._branch(seq, i) for i in range(1, num_samples)] if num_samples else []
             for sample, token in zip(samples, tokens):
-                sample.output_token_ids.append(token)
-                if sample.first_token_time is None:
-                    sample.first_token_time = now
-                reason = self._finish_reason(sample, token)
-                if reason is not None:
-                    self.cache.release(sample.seq_id, drop_reserved=sample.seq_id in pending)
-                    sample.status = SequenceStatus.FINISHED
-                    sample.finish_reason = reason
-                    sample.finish_time = now
-                    finished.append(sample)
-        if finished:
-            done = {s.seq_id for s in finished}
-            self.running = [s for s in self.running if s.seq_id not in done]
+                if self._deliver(sample, token, now, sample.seq_id in in_ahead):
+                    ended.append(sample)
+        if ended:
+            gone = {s.seq_id for s in ended}
+            self.running = [s for s in self.running if s.seq_id not in gone]
             self._nothing_admissible = False
         outputs = []
-        for request_id in dict.fromkeys(s.request_id for s in finished):
+        for request_id in dict.fromkeys(s.request_id for s in ended):
             group = self.groups[request_id]
             if len(group) == group[0].params.n and all(s.status is SequenceStatus.FINISHED for s in group):
                 outputs.append(RequestOutput(request_id, self.groups.pop(request_id)))
         return outputs
-
-    def stats(self) -> SchedulerStats:
-        return replace(self.counters, num_waiting=len(self.waiting), num_running=len(self.running))

@@ -62,7 +62,7 @@ class StepContext:
         self.state_slots: torch.Tensor = None     # int32 [S]
         self.rows: torch.Tensor = None            # int32 [R] flat rows whose logits are wanted
         self.prefill_seqs: torch.Tensor = None    # int32 [P] requests that feed more than one token (prompt portions)
-        self.tables: list[torch.Tensor] = []      # per group int32 [S, width]
+        self.tables: list[torch.Tensor] = []      # per pool of the cache manager int32 [S, width]
         lens = [b - a for a, b in zip(host.cu_q, host.cu_q[1:])]
         self.max_q_len = max(lens, default=0)     # which attention kernels a step needs is decided on the host
         self.min_q_len = min(lens, default=0)
@@ -75,7 +75,7 @@ class StepContext:
         base = self._runner.bindings[entry.cache_entry]
         if base is None:
             return None
-        table = self.tables[base.group] if base.group >= 0 else None
+        table = self.tables[self._runner.manager.pool_of_group[base.group]] if base.group >= 0 else None
         return EntryBinding(base.k_pool, base.v_pool, base.page_stride, base.entry_offset, base.page_tokens,
                             base.num_pages, table, table.shape[1] if table is not None else 0,
                             entry.writes_cache, base.group, base.state, self.state_slots)
@@ -106,7 +106,7 @@ class StepShape:
     portions: int               # entries of the list of requests that feed more than one token (0: none)
     max_q: int                  # bound on the longest portion (1: every request feeds one token)
     decodes: bool               # some request feeds exactly one token: the split-key kernels run
-    widths: tuple[int, ...]     # block-table width per layer group
+    widths: tuple[int, ...]     # block-table width per pool of the cache manager
 
 
 class _StepGraph:
@@ -210,7 +210,7 @@ class StepRunner:
         """
         The step's index data as one list of int32 words in sections (each padded to 16 bytes):
         token ids, positions, request of each token, offsets of the requests' tokens, lengths after
-        this step, wanted rows, state slots, one block table per layer group, and the requests
+        this step, wanted rows, state slots, one block table per pool of the cache manager, and the requests
         that feed more than one token.  With `shape`, every section is padded to the shape's size.
         Returns (words, offset of each section, sizes).
         """
