@@ -16,6 +16,17 @@
 //
 // The split of K depends on N and K only, never on the number of rows of x, so a row's result does
 // not depend on what else is in the batch.
+//
+// The weights' way onto the chip.  Every thread owns a ring of PJ slots in shared memory for its own
+// fragments (the 16 bytes of row r and of row r + 8 of each of its k-blocks): cp.async copies k-block
+// j into slot j % PJ, the thread reads it back into registers when its turn comes, and the slot is
+// filled again with k-block j + PJ.  Nobody else reads a thread's slots, so there is no barrier and
+// no bank conflict (a warp's slots are consecutive), and the copies in flight are bounded by shared
+// memory, not by registers.  The ring is filled BEFORE the wait for the kernel ahead on the stream:
+// the weights do not depend on that kernel, only x does, and where that kernel is a small one (a norm,
+// the combination of the attention's splits) the memory is idle meanwhile, so that the q/k/v and
+// output projections' whole matrices and a good third of the gate/up matrix are on the chip by the time
+// x arrives.
 #include "common.cuh"
 
 namespace {
@@ -42,6 +53,11 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
+                 : "memory");
+}
+
 __device__ __forceinline__ uint4 ld_stream(const void* p) {          // weights are read once: do not keep them in L1
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
@@ -57,8 +73,9 @@ template <>
 __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 // MT: tiles of 8 rows of x; WARPS: warps per CTA (the split of K); UNROLL: k-blocks a warp has in
-// flight per batch (two batches are in flight); MINB: CTAs per SM the register budget is held to.
-template <int MT, int WARPS, int EPI, typename OUT, int UNROLL, int MINB>
+// flight per batch (two batches are in flight); MINB: CTAs per SM the register budget is held to;
+// PJ: slots of each thread's ring of k-blocks in shared memory (a multiple of UNROLL): the copies in flight.
+template <int MT, int WARPS, int EPI, typename OUT, int UNROLL, int MINB, int PJ>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x, OUT* __restrict__ y,
                      int M, int N, int K, long long ldx, long long ldy, int inter, RopeArgs rope) {
@@ -104,16 +121,24 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
         for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
 
     const int kblocks = K / 32;
-    const int stride = WARPS * UNROLL;
-    // The first weights are asked for before the kernel ahead on the stream has finished: they do
-    // not depend on it.  x does, so it is read after chain_wait().  Inside the loop the next batch
-    // of weights is in flight while the current one is multiplied.
-    uint4 wl[UNROLL], wh[UNROLL];
+    // The ring is filled before the kernel ahead on the stream has finished: the weights do not depend
+    // on it.  x does, so it is read after chain_wait().
+    extern __shared__ uint4 ring[];                   // [PJ][lo, hi][thread]
+    constexpr int THREADS_ = WARPS * 32, GROUPS = PJ / UNROLL;
+    // this warp's k-blocks are j = 0, 1, ...: kb = j * WARPS + warp; `blocks` of them exist
+    const int blocks = warp < kblocks ? (kblocks - warp + WARPS - 1) / WARPS : 0;
+    auto fill = [&](int j) {                          // k-block j into its slot; beyond the last one: nothing
+        if (j < blocks) {
+            const int kb = j * WARPS + warp;
+            cp_async16(&ring[((j % PJ) * 2 + 0) * THREADS_ + threadIdx.x], w_lo + kb * 32);
+            cp_async16(&ring[((j % PJ) * 2 + 1) * THREADS_ + threadIdx.x], w_hi + kb * 32);
+        }
+    };
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-        const int kb = min(u * WARPS + warp, kblocks - 1);
-        wl[u] = ld_stream(w_lo + kb * 32);
-        wh[u] = ld_stream(w_hi + kb * 32);
+    for (int g = 0; g < GROUPS; ++g) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) fill(g * UNROLL + u);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
     if (EPI == EPI_ROPE) {
         // the token's angles and its slot in the cache: index data, read while the first weights are on their way
@@ -144,28 +169,31 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     }
     chain_wait();
     chain_release();      // after the wait: letting later kernels in sooner (before it) slowed the step by a third
-    // warp w takes the k-blocks w, w + WARPS, w + 2 WARPS, ... in that order whatever UNROLL is, so
+    // warp w takes the k-blocks w, w + WARPS, w + 2 WARPS, ... in that order whatever UNROLL and PJ are, so
     // a row's sum does not depend on the variant that the number of rows of x selects
-    for (int kb0 = warp; kb0 < kblocks; kb0 += stride) {
-        uint4 xv[UNROLL][MT], nl[UNROLL], nh[UNROLL];
+    auto load_x = [&](uint4 (&xv)[UNROLL][MT], int j0) {
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int kb = min(kb0 + u * WARPS, kblocks - 1);
+            const int kb = min((j0 + u) * WARPS + warp, kblocks - 1);
 #pragma unroll
             for (int t = 0; t < MT; ++t)
                 xv[u][t] = x_ok[t] ? *reinterpret_cast<const uint4*>(x_row[t] + kb * 32) : make_uint4(0, 0, 0, 0);
         }
-        if (kb0 + stride < kblocks) {
+    };
+    uint4 xv[UNROLL][MT], xn[UNROLL][MT];
+    if (blocks > 0) load_x(xv, 0);
+    for (int j0 = 0; j0 < blocks; j0 += UNROLL) {
+        if (j0 + UNROLL < blocks) load_x(xn, j0 + UNROLL);           // the next batch of x is on its way under this one's products
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(GROUPS - 1) : "memory");   // this batch's copies have landed
+        uint4 wl[UNROLL], wh[UNROLL];
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                const int kb = min(kb0 + stride + u * WARPS, kblocks - 1);
-                nl[u] = ld_stream(w_lo + kb * 32);
-                nh[u] = ld_stream(w_hi + kb * 32);
-            }
+        for (int u = 0; u < UNROLL; ++u) {
+            wl[u] = ring[(((j0 + u) % PJ) * 2 + 0) * THREADS_ + threadIdx.x];
+            wh[u] = ring[(((j0 + u) % PJ) * 2 + 1) * THREADS_ + threadIdx.x];
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            if (kb0 + u * WARPS < kblocks) {
+            if (j0 + u < blocks) {
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
                     mma_bf16(acc[t], wl[u].x, wh[u].x, wl[u].y, wh[u].y, xv[u][t].x, xv[u][t].y);
@@ -173,12 +201,16 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
                 }
             }
         }
+        // the slots just read are free (their values sit in registers the products above consumed): fill them again
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            wl[u] = nl[u];
-            wh[u] = nh[u];
-        }
+        for (int u = 0; u < UNROLL; ++u) fill(j0 + PJ + u);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+            for (int t = 0; t < MT; ++t) xv[u][t] = xn[u][t];
     }
+    asm volatile("cp.async.wait_all;\n" ::: "memory");
 #pragma unroll
     for (int t = 0; t < MT; ++t)
 #pragma unroll
@@ -246,23 +278,35 @@ skinny_linear_kernel(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* _
     }
 }
 
-template <int MT, int WARPS, int EPI, typename OUT, int UNROLL, int MINB>
+template <int MT, int WARPS, int EPI, typename OUT, int UNROLL, int MINB, int PJ>
 int launch(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
            cudaStream_t stream, const RopeArgs& rope) {
+    static_assert(PJ % UNROLL == 0 && PJ >= UNROLL, "the ring holds whole batches");
     const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
-    TS_CHAINED_CHECK("skinny_linear", launch_chained(skinny_linear_kernel<MT, WARPS, EPI, OUT, UNROLL, MINB>,
-                                                     dim3(tiles), dim3(WARPS * 32), 0, stream, (const __nv_bfloat16*)W,
-                                                     (const __nv_bfloat16*)x, (OUT*)y, M, N, K, ldx, ldy, inter, rope));
+    const size_t staged = (size_t)PJ * 2 * WARPS * 32 * sizeof(uint4);
+    auto kernel = skinny_linear_kernel<MT, WARPS, EPI, OUT, UNROLL, MINB, PJ>;
+    if (staged > 32 * 1024) {
+        static bool allowed = false;                   // per instantiation
+        if (!allowed) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged);
+            if (e != cudaSuccess) return ts_fail("skinny_linear: cannot reserve %zu bytes of shared memory: %s", staged,
+                                                 cudaGetErrorString(e));
+            allowed = true;
+        }
+    }
+    TS_CHAINED_CHECK("skinny_linear", launch_chained(kernel, dim3(tiles), dim3(WARPS * 32), staged, stream,
+                                                     (const __nv_bfloat16*)W, (const __nv_bfloat16*)x, (OUT*)y, M, N, K, ldx,
+                                                     ldy, inter, rope));
     return 0;
 }
 
-template <int WARPS, int EPI, typename OUT, int UNROLL, int MINB>
+template <int WARPS, int EPI, typename OUT, int UNROLL, int MINB, int PJ>
 int dispatch_m(const void* W, const void* x, void* y, int M, int N, int K, long long ldx, long long ldy, int inter,
                cudaStream_t stream, const RopeArgs& rope) {
-    if (M <= 8) return launch<1, WARPS, EPI, OUT, UNROLL, MINB>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
-    if (M <= 16) return launch<2, WARPS, EPI, OUT, UNROLL, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    if (M <= 8) return launch<1, WARPS, EPI, OUT, UNROLL, MINB, PJ>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    if (M <= 16) return launch<2, WARPS, EPI, OUT, UNROLL, 1, PJ>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
     // 32 rows of x with 16 warps: fewer loads in flight, to stay within the 128 registers a thread of 512 can have
-    return launch<4, WARPS, EPI, OUT, (WARPS > 8 ? 2 : UNROLL), 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    return launch<4, WARPS, EPI, OUT, (WARPS > 8 ? 2 : UNROLL), 1, PJ>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
 }
 
 // How a product is cut into CTAs, chosen from N and K only (never from the rows of x).  Measured on
@@ -277,10 +321,12 @@ int dispatch_warps(const void* W, const void* x, void* y, int M, int N, int K, l
                    cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
     const int tiles = EPI == EPI_SWIGLU ? (inter + 7) / 8 : (N + 15) / 16;
     const int kblocks = K / 32;
+    // Ring slots per thread (a k-block of a warp is 1 KB): 6 where seven CTAs share an SM (24 KB a CTA: over a third of a
+    // 2,048-wide tile is on the chip before the wait), 8 where two CTAs or one do (a whole 2,048-wide tile).
     if (tiles > 296 || kblocks < 32)
-        return dispatch_m<4, EPI, OUT, 2, 7>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
-    if (tiles > 148) return dispatch_m<8, EPI, OUT, 4, 2>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
-    return dispatch_m<16, EPI, OUT, 4, 1>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+        return dispatch_m<4, EPI, OUT, 2, 7, 6>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    if (tiles > 148) return dispatch_m<8, EPI, OUT, 4, 2, 8>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
+    return dispatch_m<16, EPI, OUT, 4, 1, 8>(W, x, y, M, N, K, ldx, ldy, inter, stream, rope);
 }
 
 }  // namespace
