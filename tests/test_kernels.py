@@ -76,6 +76,24 @@ def test_add_rmsnorm(ops, dtype, hidden, eps, rows):
         torch.testing.assert_close(got.cpu().double()[keep], want[[pick[i] for i in keep]], **tol(dtype, 4))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows", [6, 300])
+@pytest.mark.parametrize("hidden, vocab", [(48, 11), (2048, 1000), (777, 37)])
+def test_first_norm_gathers_the_embedding_rows_itself(ops, dtype, rows, hidden, vocab):
+    """One kernel for the embedding gather and the model's first norm: bit for bit what the two kernels give; an id outside the table is a row of zeros."""
+    table, w = rand((vocab, hidden), dtype, 5, 2.0).to(DEV), (1 + rand((hidden,), dtype, 6, 0.3)).to(dtype).to(DEV)
+    ids = torch.randint(0, vocab, (rows,), generator=torch.Generator().manual_seed(7)).tolist()
+    ids[1], ids[-1] = -1, vocab + 3
+    got, stream = ops.embed_rmsnorm(table, i32(ids), w, 1e-5)
+    rows_of = ops.embedding(table, i32(ids))
+    assert torch.equal(stream, rows_of) and torch.equal(stream[1], torch.zeros_like(stream[1]))
+    want, _ = ops.add_rmsnorm(rows_of.clone(), None, w, 1e-5)
+    assert torch.equal(got, want)
+    ok = [i for i, t in enumerate(ids) if 0 <= t < vocab]
+    ref = plain.rms_norm(table.cpu().double()[[ids[i] for i in ok]], w.cpu().double(), 1e-5, act_of(dtype))
+    torch.testing.assert_close(got.cpu().double()[ok], ref, **tol(dtype, 4))
+
+
 def test_add_rmsnorm_keeps_a_float32_weight_beside_bfloat16_rows(ops):
     x, res = rand((3, 96), torch.bfloat16, 1), rand((3, 96), torch.bfloat16, 2)
     w = 1 + rand((96,), torch.float32, 3, 0.3)

@@ -3,6 +3,9 @@
 // Reference formulas (model/llama.py:52-67): s = f32(x) + f32(residual); residual' = round(s);
 // y = s * rsqrt(mean(s^2) + eps) from the unrounded sum; out = round(y) * weight, rounded again.
 // `rows` (optional) picks the rows to normalise, output compact: the final norm of the wanted rows.
+// `gather` (optional) makes x a table whose row gather[r] is the input of row r: the token embedding
+// (model/llama.py:264, 271) read straight into the model's first norm, the row itself written out as
+// the start of the residual stream; an id outside the table reads as a row of zeros.
 #include "common.cuh"
 
 // Vector width in elements of a 16-byte access.
@@ -11,7 +14,8 @@ struct VecOf { static constexpr int N = 16 / sizeof(T); };
 
 template <typename T, typename W, bool VECTOR>
 __global__ void add_rmsnorm_kernel(const T* x, const T* residual, const W* __restrict__ weight,
-                                   T* out, T* residual_out, const int* __restrict__ rows, int hidden, float eps) {
+                                   T* out, T* residual_out, const int* __restrict__ rows, int hidden, float eps,
+                                   const int* __restrict__ gather, int gather_rows) {
     extern __shared__ float sums[];              // hidden floats: the unrounded sum, then 33 of scratch
     float* scratch = sums + hidden;
     const int r = blockIdx.x;
@@ -28,12 +32,14 @@ __global__ void add_rmsnorm_kernel(const T* x, const T* residual, const W* __res
     chain_release();
     const int src = rows ? rows[r] : r;
     if (src < 0) return;                          // a padding row
-    const T* xr = x + (long long)src * hidden;
+    const int from = gather ? gather[src] : src;
+    const bool zeros = gather && (from < 0 || from >= gather_rows);
+    const T* xr = x + (long long)(zeros ? 0 : from) * hidden;
     const T* rr = residual ? residual + (long long)src * hidden : nullptr;
     float acc = 0.f;
     if (VECTOR) {                                  // hidden is a multiple of VN and the rows are 16-byte aligned
         for (int i = threadIdx.x * VN; i < hidden; i += blockDim.x * VN) {
-            const uint4 xv = *reinterpret_cast<const uint4*>(xr + i);
+            const uint4 xv = zeros ? make_uint4(0, 0, 0, 0) : *reinterpret_cast<const uint4*>(xr + i);
             uint4 rv = make_uint4(0, 0, 0, 0);
             if (rr) rv = *reinterpret_cast<const uint4*>(rr + i);
             const T* xe = reinterpret_cast<const T*>(&xv);
@@ -48,7 +54,7 @@ __global__ void add_rmsnorm_kernel(const T* x, const T* residual, const W* __res
         }
     } else {
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-            float s = to_float<T>(xr[i]);
+            float s = zeros ? 0.f : to_float<T>(xr[i]);
             if (rr) s += to_float<T>(rr[i]);
             sums[i] = s;
             acc += s * s;
@@ -89,7 +95,8 @@ __global__ void add_rmsnorm_kernel(const T* x, const T* residual, const W* __res
 template <typename T, typename W, int TPR>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_rows_kernel(const T* x, const T* residual, const W* __restrict__ weight, T* out, T* residual_out,
-                        const int* __restrict__ rows, int num_rows, int hidden, float eps) {
+                        const int* __restrict__ rows, int num_rows, int hidden, float eps, const int* __restrict__ gather,
+                        int gather_rows) {
     constexpr int VN = VecOf<T>::N, MAXC = 8, RPC = 256 / TPR;
     __shared__ float part[8];
     const int group = threadIdx.x / TPR, member = threadIdx.x % TPR;
@@ -102,13 +109,15 @@ add_rmsnorm_rows_kernel(const T* x, const T* residual, const W* __restrict__ wei
     float s[MAXC][VN];
     float acc = 0.f;
     if (src >= 0) {
-        const T* xr = x + (long long)src * hidden;
+        const int from = gather ? gather[src] : src;
+        const bool zeros = gather && (from < 0 || from >= gather_rows);
+        const T* xr = x + (long long)(zeros ? 0 : from) * hidden;
         const T* rr = residual ? residual + (long long)src * hidden : nullptr;
         uint4 xv[MAXC], rv[MAXC];
 #pragma unroll
         for (int k = 0; k < MAXC; ++k) {
             const int c = member + k * TPR;
-            xv[k] = c < chunks ? *reinterpret_cast<const uint4*>(xr + c * VN) : make_uint4(0, 0, 0, 0);
+            xv[k] = (c < chunks && !zeros) ? *reinterpret_cast<const uint4*>(xr + c * VN) : make_uint4(0, 0, 0, 0);
             rv[k] = (rr && c < chunks) ? *reinterpret_cast<const uint4*>(rr + c * VN) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
@@ -156,7 +165,8 @@ add_rmsnorm_rows_kernel(const T* x, const T* residual, const W* __restrict__ wei
 
 template <typename T, typename W>
 static int launch(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
-                  const int* rows, int num_rows, int hidden, float eps, cudaStream_t stream) {
+                  const int* rows, int num_rows, int hidden, float eps, const int* gather, int gather_rows,
+                  cudaStream_t stream) {
     const bool vector = hidden % VecOf<T>::N == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 &&
                         (residual == nullptr || (uintptr_t)residual % 16 == 0) &&
                         (residual_out == nullptr || (uintptr_t)residual_out % 16 == 0);
@@ -169,7 +179,7 @@ static int launch(const void* x, const void* residual, const void* weight, void*
 #define TS_NORM_ROWS(TPR_)                                                                                              \
     TS_CHAINED_CHECK("add_rmsnorm", launch_chained(add_rmsnorm_rows_kernel<T, W, TPR_>, grid, dim3(256), 0, stream,     \
                                                    (const T*)x, (const T*)residual, (const W*)weight, (T*)out,          \
-                                                   (T*)residual_out, rows, num_rows, hidden, eps))
+                                                   (T*)residual_out, rows, num_rows, hidden, eps, gather, gather_rows))
             if (tpr == 32) TS_NORM_ROWS(32);
             else if (tpr == 64) TS_NORM_ROWS(64);
             else TS_NORM_ROWS(128);
@@ -189,22 +199,24 @@ static int launch(const void* x, const void* residual, const void* weight, void*
     }
     TS_CHAINED_CHECK("add_rmsnorm", launch_chained(kernel, dim3(num_rows), dim3(threads), smem, stream, (const T*)x,
                                                    (const T*)residual, (const W*)weight, (T*)out, (T*)residual_out,
-                                                   rows, hidden, eps));
+                                                   rows, hidden, eps, gather, gather_rows));
     return 0;
 }
 
 TS_API int ts_add_rmsnorm(const void* x, const void* residual, const void* weight, void* out, void* residual_out,
                           const int* rows, int num_rows, int hidden, float eps, int dtype, int weight_dtype,
-                          cudaStream_t stream) {
+                          const int* gather, int gather_rows, cudaStream_t stream) {
+    TS_REQUIRE(gather == nullptr || (gather_rows > 0 && residual == nullptr && rows == nullptr),
+               "add_rmsnorm: a gathered input starts the stream (no residual, no row choice) from a table with rows");
     TS_REQUIRE(num_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d H=%d", num_rows, hidden);
     TS_REQUIRE(hidden <= 56 * 1024, "add_rmsnorm: hidden size %d exceeds the kernel's limit of 57344", hidden);
     TS_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
     if (num_rows == 0) return 0;
     if (dtype == TS_F32 && weight_dtype == TS_F32)
-        return launch<float, float>(x, residual, weight, out, residual_out, rows, num_rows, hidden, eps, stream);
+        return launch<float, float>(x, residual, weight, out, residual_out, rows, num_rows, hidden, eps, gather, gather_rows, stream);
     if (dtype == TS_BF16 && weight_dtype == TS_BF16)
-        return launch<__nv_bfloat16, __nv_bfloat16>(x, residual, weight, out, residual_out, rows, num_rows, hidden, eps, stream);
+        return launch<__nv_bfloat16, __nv_bfloat16>(x, residual, weight, out, residual_out, rows, num_rows, hidden, eps, gather, gather_rows, stream);
     if (dtype == TS_BF16 && weight_dtype == TS_F32)
-        return launch<__nv_bfloat16, float>(x, residual, weight, out, residual_out, rows, num_rows, hidden, eps, stream);
+        return launch<__nv_bfloat16, float>(x, residual, weight, out, residual_out, rows, num_rows, hidden, eps, gather, gather_rows, stream);
     return ts_fail("add_rmsnorm: unsupported dtypes activation=%d weight=%d", dtype, weight_dtype);
 }

@@ -38,7 +38,7 @@ _SIGNATURES = {
     "ts_last_error": ("const char*", ""),
     "ts_abi_version": ("int", ""),
     "ts_set_chaining": ("void", "i"),
-    "ts_add_rmsnorm": ("int", "ppppppiifiip"),
+    "ts_add_rmsnorm": ("int", "ppppppiifiipip"),
     "ts_copy_page_slots": ("int", "ppiiiiiiiiip"),
     "ts_rope_store": ("int", "ppppiipipplliiiiiiiip"),
     "ts_sample_scratch_words": ("int", "ii"),
@@ -265,8 +265,26 @@ class Ops:
             new_residual, residual_out = residual, None
         self._call("ts_add_rmsnorm", _ptr(x), _ptr(residual), _ptr(weight), _ptr(out), _ptr(residual_out), _ptr(rows),
                    count, hidden, eps, _DTYPE_CODE[x.dtype],
-                   _DTYPE_CODE[weight.dtype], _stream())
+                   _DTYPE_CODE[weight.dtype], 0, 0, _stream())
         return out, new_residual
+
+    def embed_rmsnorm(self, table: torch.Tensor, ids: torch.Tensor, weight: torch.Tensor, eps: float) -> tuple[torch.Tensor, torch.Tensor]:
+        """
+        (normalised, residual stream) of the model's first norm with the token embedding read straight
+        into it: row t of the stream is table[ids[t]] (zeros for an id outside the table), one kernel
+        instead of a gather and a norm.
+        """
+        self._check(table, "embedding table", tuple(_DTYPE_CODE), 2)
+        self._check(ids, "token ids", torch.int32, 1)
+        self._check(weight, "norm weight", tuple(_DTYPE_CODE), 1)
+        hidden = table.shape[1]
+        if weight.shape[0] != hidden:
+            raise KernelError(f"norm weight has {weight.shape[0]} elements for rows of {hidden}")
+        out = torch.empty((ids.shape[0], hidden), dtype=table.dtype, device=table.device)
+        stream = torch.empty_like(out)
+        self._call("ts_add_rmsnorm", _ptr(table), 0, _ptr(weight), _ptr(out), _ptr(stream), 0, ids.shape[0], hidden, eps,
+                   _DTYPE_CODE[table.dtype], _DTYPE_CODE[weight.dtype], _ptr(ids), table.shape[0], _stream())
+        return out, stream
 
     def rope_store(self, qkv: torch.Tensor, ctx, binding, table: torch.Tensor | None, nh: int, nkv: int, hd: int) -> None:
         self._check(qkv, "qkv", tuple(_DTYPE_CODE), 2)

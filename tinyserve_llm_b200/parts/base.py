@@ -69,6 +69,13 @@ class Norm(Part):
                 rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         raise NotImplementedError
 
+    def forward_embedded(self, table: torch.Tensor, ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """
+        The model's first norm: its input rows are table[ids], which start the residual stream.
+        A norm whose kernel can gather overrides this and saves the separate embedding kernel.
+        """
+        return self.forward(self.rt.ops.embedding(table, ids), None)
+
 
 class PositionEncoding(Part):
     """

@@ -21,6 +21,8 @@ def _sub(tensors: dict[str, torch.Tensor], prefix: str) -> dict[str, torch.Tenso
 class PreNormBlock:
     """x = x + mixer(norm1(x)); x = x + ffn(norm2(x)), with both adds fused into the next norm."""
 
+    takes_token_ids = True        # forward(..., embedding=table): x holds token ids, the first norm gathers the rows
+
     @classmethod
     def declare(cls, spec: BlockSpec) -> dict[str, TensorDecl]:
         """Names local to the block's prefix."""
@@ -45,8 +47,12 @@ class PreNormBlock:
                  for role, part, prefix in self._members(spec)]
         self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward = built
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor | None, ctx, binding):
-        x, residual = self.mixer_norm.forward(x, residual)
+    def forward(self, x: torch.Tensor, residual: torch.Tensor | None, ctx, binding, embedding: torch.Tensor | None = None):
+        """`embedding`: this is the model's first block and `x` holds token ids, rows of that table."""
+        if embedding is not None:
+            x, residual = self.mixer_norm.forward_embedded(embedding, x)
+        else:
+            x, residual = self.mixer_norm.forward(x, residual)
         x = self.mixer.forward(x, ctx, binding)
         x, residual = self.feed_forward_norm.forward(x, residual)
         x = self.feed_forward.forward(x, ctx)

@@ -83,9 +83,15 @@ class DecoderModel:
 
     def forward(self, ctx) -> tuple[torch.Tensor, torch.Tensor | None]:
         """Runs the step's tokens through the run list; returns (last branch output, residual stream)."""
-        x = self.rt.ops.embedding(self.embedding, ctx.token_ids)
-        residual = None
-        for entry in self.spec.run:
+        # an arrangement that takes the embedding table reads the token ids itself (its first norm gathers the rows)
+        run = self.spec.run
+        first = self.blocks[run[0].block] if run else None
+        if first is not None and getattr(first, "takes_token_ids", False):
+            x, residual = first.forward(ctx.token_ids, None, ctx, ctx.binding(run[0]), embedding=self.embedding)
+            run = run[1:]
+        else:
+            x, residual = self.rt.ops.embedding(self.embedding, ctx.token_ids), None
+        for entry in run:
             x, residual = self.blocks[entry.block].forward(x, residual, ctx, ctx.binding(entry))
         return x, residual
 

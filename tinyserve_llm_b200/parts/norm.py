@@ -36,3 +36,6 @@ class RMSNorm(Norm):
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None,
                 rows: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
         return self.rt.ops.add_rmsnorm(x, residual, self.weight, self.eps, rows)
+
+    def forward_embedded(self, table: torch.Tensor, ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        return self.rt.ops.embed_rmsnorm(table, ids, self.weight, self.eps)
