@@ -283,6 +283,34 @@ def run_ours(args) -> dict:
 
     for i in range(3):
         prefill_once(i)
+    if args.timeline:
+        # Where a decode step's time goes inside the replayed graph, overlaps of chained kernels included: CUPTI's
+        # record of every kernel of the last of three steps (start after the step's first kernel, duration, and how
+        # long after the end of everything before it the kernel itself ended: its share of the critical path).
+        from torch.profiler import ProfilerActivity, profile
+        temps = torch.zeros(BATCH, dtype=torch.float32, device=llm.device)
+        keys = torch.zeros((BATCH, 2), dtype=torch.int32, device=llm.device)
+        with held_contexts(BATCH, CONTEXT) as entries:
+            for _ in range(3):
+                ops.sample(runner.step(entries), temps, keys)
+            torch.cuda.synchronize()
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for _ in range(3):
+                    ops.sample(runner.step(entries), temps, keys)
+                torch.cuda.synchronize()
+        events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+                         and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()),
+                        key=lambda e: e.time_range.start)
+        last = events[-(len(events) // 3):]
+        origin, done = last[0].time_range.start, last[0].time_range.start
+        print(f"# one decode step, batch {BATCH}, contexts of {CONTEXT} tokens, {layers} layers: {len(last)} kernels")
+        print("#  start us   length us   ends after all before it (us)   kernel")
+        for e in last:
+            print(f"{e.time_range.start - origin:10.2f} {e.time_range.end - e.time_range.start:11.2f} "
+                  f"{max(0.0, e.time_range.end - done):12.2f}   {e.name[:90]}")
+            done = max(done, e.time_range.end)
+        print(f"# the step: {done - origin:.1f} us")
+        return {"impl": "ours", "profiled": "timeline of one decode step", "config": {"model": model_name, "layers": layers}}
     if args.profile_step is not None:
         if args.profile_step == "prefill":
             torch.cuda.profiler.start()
@@ -501,6 +529,9 @@ def main() -> int:
     parser.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
                         help="no measurement: warm up, then run ONE step of that kind between cudaProfilerStart and "
                              "cudaProfilerStop (for `ncu --profile-from-start off`), and exit")
+    parser.add_argument("--timeline", action="store_true",
+                        help="no measurement: print every kernel of one decode step with its start, length and its share of the "
+                             "critical path inside the replayed graph (CUPTI through torch.profiler), and exit")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (run with --gpus 1)")

@@ -130,6 +130,10 @@ class Ops:
         # epilogue (10 to 20 % faster than the library product plus an activation kernel from 1,536 rows on a B200);
         # below it the library product wins, whose tiles fit a few row tiles better.
         self.tcgen05_swiglu_min_rows = int(os.environ.get("TINYSERVE_B200_SWIGLU_ROWS", "1408"))
+        # up to this many rows the gate/up product with SwiGLU runs on the decode product (measured on a B200 with Llama
+        # 3.2 1B's sizes, whole decode steps: 4 to 6 % faster than the library product plus the activation kernel at 12,
+        # 16, 24 and 32 rows, since the weights go through the cp.async ring)
+        self.swiglu_skinny_rows = self.skinny_max_rows
 
     def set_chaining(self, enabled: bool) -> None:
         self.chaining = bool(enabled)
@@ -474,10 +478,7 @@ class Ops:
         self._check(gate_up_weight, "weight", x.dtype, 2)
         if gate_up_weight.shape[0] % 2 or x.shape[1] != gate_up_weight.shape[1]:
             raise KernelError("linear_swiglu: the weight must hold gate and up halves over x's columns")
-        # the decode product serves up to 8 rows here: from 9 rows on, its CTAs (two or four tiles of x each) no longer
-        # fit the SMs in one wave for a matrix of this many rows, and the library product plus the activation
-        # kernel is faster (18 against 15 us at 16 rows of Llama 3.2 1B's sizes on a B200)
-        if not (self._skinny(x, gate_up_weight) and x.shape[0] <= 8):
+        if not (self._skinny(x, gate_up_weight) and x.shape[0] <= self.swiglu_skinny_rows):
             if x.dtype == torch.bfloat16 and x.shape[0] >= self.tcgen05_swiglu_min_rows and self.lib.ts_gemm_tcgen05_supported(
                     _ptr(gate_up_weight), _ptr(x), x.shape[0], gate_up_weight.shape[0], x.shape[1],
                     x.shape[1]):
