@@ -318,8 +318,8 @@ def test_decode_graphs_follow_the_longest_request(model_folders, dtype):
 def test_steps_with_prompt_portions_are_replayed_from_graphs(model_folders, name, dtype, page):
     """
     Three requests decode while two more arrive in portions of 40 and 24 tokens (the last portions are
-    shorter): from the second time a shape of step is met it is captured and replayed, padded to its
-    buckets.  float32 gives bit for bit what steps launched kernel by kernel give; bfloat16 the same
+    shorter): from the second time a shape of step is met (the runner is told so here; its default is the
+    third) it is captured and replayed, padded to its buckets.  float32 gives bit for bit what steps launched kernel by kernel give; bfloat16 the same
     up to the library product's choice of kernel for another number of rows.
     """
     from tinyserve_llm_b200.engine.loading import build_cache, load_model
@@ -332,7 +332,7 @@ def test_steps_with_prompt_portions_are_replayed_from_graphs(model_folders, name
     outs = {}
     for graphs in (True, False):
         _, manager, storage = build_cache(model, page, 40, caching=False)
-        runner = StepRunner(model, manager, storage, cuda_graphs=graphs)
+        runner = StepRunner(model, manager, storage, cuda_graphs=graphs, sightings_before_capture=2)
         for i, p in enumerate(decoding):
             assert manager.admit(i, p)
         runner.step([StepEntry(i, p, []) for i, p in enumerate(decoding)])

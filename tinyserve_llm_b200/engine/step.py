@@ -132,9 +132,12 @@ class StepRunner:
       attention's grid covers what the tables can hold, and tables for the longest context the
       engine allows made 64 requests of 512 tokens cost 3.4 ms a step instead of 1.26);
     * steps with prompt portions of up to `graph_max_tokens` tokens in all: tokens in multiples of
-      64 (128 from 512 on), requests, portions and the longest portion in powers of two.  Launched
-      kernel by kernel such a step costs about 2 ms of host time whatever its size, more than its
-      device time below a few hundred tokens.  A shape is captured when it is met the second time.
+      64, requests, portions and the longest portion in powers of two.  Launched kernel by kernel
+      such a step costs about 2 ms of host time whatever its size, more than its device time below
+      a few hundred tokens (Llama 3.2 1B sizes); from about 512 tokens on the device takes longer
+      than the host and a graph gains nothing.  A capture costs several steps' time, so a shape is
+      captured when it is met the third time: a replay of conversations whose prompts all differ
+      in length met two thirds of its shapes once or twice only.
 
     Larger steps, steps that want more logits rows than they have requests, and models with a part
     that is not graph safe run eagerly.  The logits a replayed step returns live in one static
@@ -148,7 +151,8 @@ class StepRunner:
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: DeviceCacheStorage, *,
                  cuda_graphs: bool = True, max_decode_batch: int = 256, max_model_len: int | None = None,
-                 max_graphs: int = 64, table_pages: Sequence[int] | None = None, graph_max_tokens: int = 1024) -> None:
+                 max_graphs: int = 64, table_pages: Sequence[int] | None = None, graph_max_tokens: int = 512,
+                 sightings_before_capture: int = 3) -> None:
         self.model = model
         self.manager = manager
         self.storage = storage
@@ -160,6 +164,7 @@ class StepRunner:
         self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
         self.max_decode_batch = max_decode_batch
         self.graph_max_tokens = graph_max_tokens
+        self.sightings_before_capture = sightings_before_capture
         longest = min(max_model_len or model.spec.max_positions, model.spec.max_positions)
         pool_pages = list(table_pages) if table_pages is not None else [pool.num_pages for pool in manager.pools]
         self._graph_widths = [max(1, min(pages, -(-longest // manager.page_tokens))) for pages in pool_pages]
@@ -345,11 +350,13 @@ class StepRunner:
             if captured is not None:
                 self._graphs[shape] = captured               # most recently used last
                 return self._replay(captured, entries, device_tokens)
-            if shape.portions == 0 or self._met.pop(shape, 0) >= 1:
+            met = self._met.get(shape, 0) + 1
+            if shape.portions == 0 or met >= self.sightings_before_capture:
+                self._met.pop(shape, None)
                 return self._replay(self._capture(entries, shape, device_tokens), entries, None, launched=True)
             if len(self._met) > 4 * self.max_graphs:
                 self._met.clear()
-            self._met[shape] = 1
+            self._met[shape] = met
         ctx = self._pack(entries)
         if device_tokens is not None:
             self.model.rt.ops.feed_tokens(ctx.token_ids, device_tokens)
@@ -399,8 +406,7 @@ class StepRunner:
             return StepShape(seqs, seqs, 0, 1, True, widths)
         if tokens > self.graph_max_tokens:
             return None
-        step = 64 if tokens <= 512 else 128
-        padded = -(-tokens // step) * step
+        padded = -(-tokens // 64) * 64
         return StepShape(padded, seqs, _power_of_two(portions), min(padded, max(64, _power_of_two(longest))), decodes, widths)
 
     def _replay(self, captured: _StepGraph, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None,
@@ -427,8 +433,9 @@ class StepRunner:
             self._graph_logits = torch.empty((self.bucket(self.max_decode_batch), self.model.spec.vocab_size),
                                              dtype=torch.float32, device=self.device)
         out = self._graph_logits[:shape.seqs]
-        # once eagerly: libraries create their handles and workspaces outside the capture; the
-        # step's keys and values are written by this run and again, identically, by the replay
+        # once eagerly: libraries create their handles and workspaces outside the capture, and this run IS
+        # the step (its keys and values are written, its logits are in the static buffer); the capture
+        # that follows records the same launches without running them
         x, residual = self.model.forward(ctx)
         self.model.logits(x, residual, ctx.rows, out=out)
         torch.cuda.synchronize(self.device)
@@ -441,7 +448,6 @@ class StepRunner:
             x, residual = self.model.forward(ctx)
             logits = self.model.logits(x, residual, ctx.rows, out=out)
         launches = ops.launches - before
-        graph.replay()
         captured = _StepGraph(graph, index_buffer, logits, shape, launches)
         while len(self._graphs) >= self.max_graphs:
             self._graphs.pop(next(iter(self._graphs)))
