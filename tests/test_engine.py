@@ -92,18 +92,60 @@ def test_running_out_of_pages_preempts_and_changes_no_token(model_folders, cachi
     assert llm.cache.stats().pages_in_use == 0
 
 
-def test_bfloat16_generation_stays_with_the_plain_bfloat16_model(model_folders, workload_b):
-    """Token parity is not exact in bfloat16 (near-tied logits); what a token costs in logit is bounded instead."""
-    prompts, _ = workload_b
-    cfg, tensors = plain.read_model_folder(model_folders["b"])
-    llm = make_llm(model_folders["b"], PAGE_B, dtype="bfloat16")
-    done = llm.generate(prompts[:4], greedy(6))
+def token_costs_within_bound(cfg, tensors, prompt, tokens, act="bfloat16"):
+    """
+    Token parity is not exact in bfloat16 (near-tied logits), so what each generated token costs in
+    plain logit is bounded instead.  The replay tests hold every engine logit to the plain one
+    within d = 1.2 % of the largest logit; a token that is the largest of the engine's logits can
+    then lie at most 2 d under the largest plain logit (its own logit may be d too high, the plain
+    winner's d too low).
+    """
+    ids = list(prompt)
+    for token in tokens:
+        row = plain.logits(cfg, tensors, ids, act)[-1]
+        if row.max().item() - row[token].item() > 2 * 0.012 * row.abs().max().item():
+            return False
+        ids.append(token)
+    return True
+
+
+@pytest.mark.parametrize("name, page, kwargs", [
+    ("b", PAGE_B, {}), ("d", 64, {}), ("d", 64, {"cuda_graphs": False, "run_ahead": False}),
+    ("d", 64, {"prefill_chunk": 24, "max_num_batched_tokens": 40}), ("d", 64, {"num_blocks": 7, "caching": False}),
+    ("d", 64, {"caching": False, "run_ahead": False})])
+def test_bfloat16_generation_stays_with_the_plain_bfloat16_model(model_folders, name, page, kwargs):
+    """
+    bfloat16 through the whole engine: CUDA-graph decode and steps launched ahead (the default), neither,
+    prompts in small portions beside decodes, and a pool so small that requests are preempted and run again.
+    """
+    raw = {"b": TINY_B, "d": TINY_D}[name]
+    vocab = raw["vocab_size"]
+    stem = ru.random_ids(vocab, 70, 17)
+    prompts = [stem + ru.random_ids(vocab, 9, 18), ru.random_ids(vocab, 3, 19), stem[:50] + ru.random_ids(vocab, 30, 20),
+               ru.random_ids(vocab, 130, 21)]
+    cfg, tensors = plain.read_model_folder(model_folders[name])
+    llm = make_llm(model_folders[name], page, dtype="bfloat16", max_model_len=260, **kwargs)
+    done = llm.generate(prompts, greedy(70 if "num_blocks" in kwargs else 8))      # 70: the requests outgrow the small pool
     for prompt, c in zip(prompts, done):
-        ids = list(prompt)
-        for token in c.token_ids[0]:
-            row = plain.logits(cfg, tensors, ids, "bfloat16")[-1]
-            assert row.max().item() - row[token].item() <= 0.012 * row.abs().max().item() * 2
-            ids.append(token)
+        assert token_costs_within_bound(cfg, tensors, prompt, c.token_ids[0][:8]), (kwargs, c.token_ids[0])
+    assert llm.cache.stats().pages_in_use == 0
+    if "num_blocks" in kwargs:
+        assert llm.scheduler.stats().preemptions > 0, "the pool was meant to be too small"
+    if kwargs.get("cuda_graphs", True):
+        assert llm.runner.graph_replays > 0
+    if kwargs.get("run_ahead", True):
+        assert llm.steps_launched_ahead > 0
+
+
+def test_bfloat16_forks_share_and_copy_pages(model_folders):
+    """n = 3 greedy samples of one prompt in bfloat16: the same tokens three times (the forks read the same pages and logits), within the bound."""
+    prompt = ru.random_ids(TINY_D["vocab_size"], 75, 23)
+    llm = make_llm(model_folders["d"], 64, dtype="bfloat16", max_model_len=260)
+    done = llm.generate([prompt], greedy(10, n=3))[0]
+    assert done.token_ids[0] == done.token_ids[1] == done.token_ids[2]
+    cfg, tensors = plain.read_model_folder(model_folders["d"])
+    assert token_costs_within_bound(cfg, tensors, prompt, done.token_ids[0][:6])
+    assert llm.cache.stats().cow_copies >= 2 and llm.cache.stats().pages_in_use == 0
 
 
 def test_forks_agree_when_greedy_and_leave_no_page_behind(model_folders):
@@ -370,6 +412,38 @@ def test_steps_with_prompt_portions_are_replayed_from_graphs(model_folders, name
             assert torch.equal(a, b)
         else:
             torch.testing.assert_close(a, b, atol=0.012 * float(b.abs().max()), rtol=0.0)
+
+
+def test_a_captured_step_records_no_buffer_of_the_eager_run(model_folders):
+    """
+    A capture runs the step once eagerly, then records it.  Scratch buffers that the parts keep in the step's
+    context during the eager run belong to the ordinary allocator and are freed with the context: the recorded
+    launches must get buffers of their own (from the graphs' pool), or a replay writes into freed memory.
+    """
+    from tinyserve_llm_b200.engine.loading import build_cache, load_model
+    from tinyserve_llm_b200.engine.step import StepEntry, StepRunner
+    model = load_model(model_folders["d"], "bfloat16", "cuda")
+    _, manager, storage = build_cache(model, 64, 8, caching=False)
+    runner = StepRunner(model, manager, storage)
+    assert manager.admit(0, ru.random_ids(TINY_D["vocab_size"], 70, 5))
+    runner.step([StepEntry(0, manager.seqs[0].tokens, [])])
+    manager.commit(0, 70)
+    manager.extend(0, [9])
+    seen = []
+    forward = model.forward
+
+    def spy(ctx):
+        seen.append((torch.cuda.is_current_stream_capturing(), dict(ctx.scratch)))
+        return forward(ctx)
+
+    model.forward = spy
+    try:
+        runner.step([StepEntry(0, [9], [0])])                  # the first decode step: eager run, then capture
+    finally:
+        model.forward = forward
+    assert [capturing for capturing, _ in seen] == [False, True]
+    assert seen[1][1] == {}, "the capture began with the eager run's scratch buffers"
+    assert runner.graph_replays == 1
 
 
 def test_multi_turn_replay_reuses_histories_and_changes_no_token(model_folders, tmp_path):

@@ -439,6 +439,12 @@ class StepRunner:
         x, residual = self.model.forward(ctx)
         self.model.logits(x, residual, ctx.rows, out=out)
         torch.cuda.synchronize(self.device)
+        # Scratch buffers the parts put into the context during the eager run came from the ordinary allocator and
+        # go back to it when this context is dropped: the capture must not record their addresses (a replay would
+        # write into memory that by then belongs to someone else, or to nobody).  It allocates its own, from the
+        # graphs' pool.
+        del x, residual
+        ctx.scratch.clear()
         graph = torch.cuda.CUDAGraph()
         ops = self.model.rt.ops
         before = ops.launches
