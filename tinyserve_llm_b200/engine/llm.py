@@ -23,7 +23,7 @@ from tinyserve_llm_b200.cache.storage import DeviceCacheStorage
 from tinyserve_llm_b200.engine.loading import build_cache, load_model, require_cuda, resolve_dtype
 from tinyserve_llm_b200.engine.scheduler import RequestOutput, ScheduledSeq, Scheduler, SchedulerConfig, SchedulerStats
 from tinyserve_llm_b200.engine.sequence import SamplingParams, SequenceStatus
-from tinyserve_llm_b200.engine.step import StepEntry, StepRunner, StepShape
+from tinyserve_llm_b200.engine.step import GRAPH_MAX_TOKENS, StepEntry, StepRunner, StepShape
 from tinyserve_llm_b200.sampling.sampler import PendingTokens, Sampler
 
 logger = logging.getLogger(__name__)
@@ -155,7 +155,7 @@ class LLM:
         device = self.device
         seqs = min(cfg.max_num_seqs, cfg.max_num_batched_tokens)
         each = max(1, min(cfg.max_num_batched_tokens // seqs, cfg.max_model_len - 1, cfg.prefill_chunk or (1 << 30)))
-        limit = StepRunner.__init__.__kwdefaults__["graph_max_tokens"]      # the largest step with a portion that a graph takes
+        limit = GRAPH_MAX_TOKENS                                            # the largest step with a portion that a graph takes
         portion = max(0, min(limit - (seqs - 1), cfg.max_model_len - each - 3, cfg.prefill_chunk or limit))
         pages = seqs * -(-(each + 2) // page) + -(-portion // page) + 2
         _, manager, storage = build_cache(self.model, page, pages, caching=False, num_state_slots=max(state_slots, 1))

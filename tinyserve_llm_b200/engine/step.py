@@ -81,6 +81,9 @@ class StepContext:
                             entry.writes_cache, base.group, base.state, self.state_slots)
 
 
+GRAPH_MAX_TOKENS = 512      # the largest step with a prompt portion that is replayed from a graph (see StepRunner)
+
+
 def _pad4(n: int) -> int:
     return (n + 3) & ~3
 
@@ -151,7 +154,7 @@ class StepRunner:
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: DeviceCacheStorage, *,
                  cuda_graphs: bool = True, max_decode_batch: int = 256, max_model_len: int | None = None,
-                 max_graphs: int = 64, table_pages: Sequence[int] | None = None, graph_max_tokens: int = 512,
+                 max_graphs: int = 64, table_pages: Sequence[int] | None = None, graph_max_tokens: int = GRAPH_MAX_TOKENS,
                  sightings_before_capture: int = 3) -> None:
         self.model = model
         self.manager = manager
