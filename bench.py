@@ -172,12 +172,19 @@ def kv_bytes(cfg: dict, layers: int, batch: int, context: int) -> int:
     return batch * context * 2 * layers * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
 
 
-def prefill_flops(cfg: dict, layers: int, tokens: int) -> float:
+def prefill_flops(cfg: dict, layers: int, tokens: int, before: int = 0) -> float:
+    """A prompt portion of `tokens` tokens behind `before` cached ones, the logits of its last token wanted."""
     h, i, hd = cfg["hidden_size"], cfg["intermediate_size"], cfg["head_dim"]
     nh, nkv, v = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["vocab_size"]
     gemm = 2.0 * tokens * (h * (nh + 2 * nkv) * hd + nh * hd * h + 3 * i * h)
-    attention = 2.0 * 2.0 * nh * hd * tokens * (tokens + 1) / 2.0
+    attention = 2.0 * 2.0 * nh * hd * tokens * (before + (tokens + 1) / 2.0)
     return layers * (gemm + attention) + 2.0 * v * h
+
+
+# --sweep: decode steps (batch, context) and prompt portions (tokens, cached tokens before them)
+SWEEP_DECODE = [(1, 512), (1, 4096), (1, 32768), (1, 131072 - 64), (8, 512), (8, 4096), (8, 32768),
+                (64, 512), (64, 4096), (64, 16384)]
+SWEEP_PREFILL = [(512, 0), (2048, 0), (8192, 0), (8192, 24576), (8192, 122880 - 64)]
 
 
 def run_ours(args) -> dict:
@@ -197,6 +204,9 @@ def run_ours(args) -> dict:
     steps, warmup = args.steps, max(args.warmup, 3)
     max_len = CONTEXT + steps + warmup + 64 + 512
     pages = 66 * (-(-max_len // PAGE) + 1) + 16
+    if args.sweep:
+        max_len = cfg["max_position_embeddings"]
+        pages = max(b * (c // PAGE + 2) for b, c in SWEEP_DECODE) + 16
     llm = LLM(folder, SchedulerConfig(max_model_len=max_len, max_num_seqs=96, max_num_batched_tokens=8192,
                                       prefill_chunk=2048, watermark=0.0),
               CacheConfig(block_size=PAGE, caching=False), dtype="bfloat16", num_blocks=pages, seed=0,
@@ -268,29 +278,61 @@ def run_ours(args) -> dict:
             return begin.elapsed_time(end) / k, ops.launches - before
 
     # ---- prefill of 2,048 tokens, whole, device timed
-    def prefill_once(seq_id: int) -> float:
-        tokens = prompts(1, PREFILL_TOKENS)[0]
-        assert cache.admit(("prefill", seq_id), tokens)
+    def prefill_once(seq_id: int, count: int = PREFILL_TOKENS, before: int = 0) -> float:
+        """One prompt portion of `count` tokens behind `before` tokens of the same request (fed untimed, in portions)."""
+        tokens = prompts(1, before + count)[0]
+        name = ("prefill", seq_id)
+        for at in range(0, before, 8192):
+            part = tokens[at:min(at + 8192, before)]
+            if at == 0:
+                assert cache.admit(name, part), "the cache pool is too small for the measurement"
+            else:
+                cache.extend(name, part)
+            runner.step([StepEntry(name, part, [])])
+            cache.commit(name, len(part))
+        if before:
+            cache.extend(name, tokens[before:])
+        else:
+            assert cache.admit(name, tokens)
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         begin.record()
-        runner.step([StepEntry(("prefill", seq_id), tokens, [PREFILL_TOKENS - 1])])
+        runner.step([StepEntry(name, tokens[before:], [count - 1])])
         end.record()
         torch.cuda.synchronize()
-        cache.commit(("prefill", seq_id), PREFILL_TOKENS)
-        cache.release(("prefill", seq_id))
+        cache.commit(name, count)
+        cache.release(name)
         return begin.elapsed_time(end)
 
     for i in range(3):
         prefill_once(i)
+    if args.sweep:
+        peak, peak_kind = peaks()
+        decode, prefill = [], []
+        with ClockSampler() as clocks:
+            for b, c in SWEEP_DECODE:
+                ms, _ = device_decode(b, c, 20, 3)
+                moved = weight_bytes(cfg, layers) + kv_bytes(cfg, layers, b, c)
+                decode.append({"batch": b, "context": c, "ms": round(ms, 4), "value": round(b / ms * 1e3, 1),
+                               "hbm_frac": round(moved / (ms * 1e-3) / 1e9 / peak["hbm_gbs"], 4)})
+            for n, (count, before) in enumerate(SWEEP_PREFILL):
+                prefill_once(100 + 10 * n, count, before)
+                ms = statistics.median(prefill_once(101 + 10 * n + i, count, before) for i in range(3))
+                flops = prefill_flops(cfg, layers, count, before)
+                prefill.append({"tokens": count, "cached_before": before, "ms": round(ms, 3),
+                                "value": round(count / ms * 1e3, 1),
+                                "frac": round(flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)})
+        return {"impl": "ours", "sweep": {"decode": decode, "prefill": prefill, "unit": "tokens/s", "peaks": peak_kind},
+                "config": size_config(cfg, model_name, layers, full_layers), "clocks": clocks.summary()}
     if args.timeline:
         # Where a decode step's time goes inside the replayed graph, overlaps of chained kernels included: CUPTI's
         # record of every kernel of the last of three steps (start after the step's first kernel, duration, and how
         # long after the end of everything before it the kernel itself ended: its share of the critical path).
         from torch.profiler import ProfilerActivity, profile
-        temps = torch.zeros(BATCH, dtype=torch.float32, device=llm.device)
-        keys = torch.zeros((BATCH, 2), dtype=torch.int32, device=llm.device)
-        with held_contexts(BATCH, CONTEXT) as entries:
+        tl_batch, tl_context = (int(v) for v in args.timeline.split("x"))
+        temps = torch.zeros(tl_batch, dtype=torch.float32, device=llm.device)
+        keys = torch.zeros((tl_batch, 2), dtype=torch.int32, device=llm.device)
+        with held_contexts(tl_batch, tl_context) as entries:
             for _ in range(3):
                 ops.sample(runner.step(entries), temps, keys)
             torch.cuda.synchronize()
@@ -303,7 +345,7 @@ def run_ours(args) -> dict:
                         key=lambda e: e.time_range.start)
         last = events[-(len(events) // 3):]
         origin, done = last[0].time_range.start, last[0].time_range.start
-        print(f"# one decode step, batch {BATCH}, contexts of {CONTEXT} tokens, {layers} layers: {len(last)} kernels")
+        print(f"# one decode step, batch {tl_batch}, contexts of {tl_context} tokens, {layers} layers: {len(last)} kernels")
         print("#  start us   length us   ends after all before it (us)   kernel")
         for e in last:
             print(f"{e.time_range.start - origin:10.2f} {e.time_range.end - e.time_range.start:11.2f} "
@@ -529,9 +571,14 @@ def main() -> int:
     parser.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
                         help="no measurement: warm up, then run ONE step of that kind between cudaProfilerStart and "
                              "cudaProfilerStop (for `ncu --profile-from-start off`), and exit")
-    parser.add_argument("--timeline", action="store_true",
-                        help="no measurement: print every kernel of one decode step with its start, length and its share of the "
-                             "critical path inside the replayed graph (CUPTI through torch.profiler), and exit")
+    parser.add_argument("--sweep", action="store_true",
+                        help="instead of the headline record: decode steps at batch 1, 8 and 64 with contexts from 512 tokens to "
+                             "the model's longest, and prompt portions of 512 to 8,192 tokens behind up to 120k cached tokens, "
+                             "each with its fraction of the measured peak")
+    parser.add_argument("--timeline", nargs="?", const=f"{BATCH}x{CONTEXT}", default=None, metavar="BATCHxCONTEXT",
+                        help="no measurement: print every kernel of one decode step (default: the headline's batch and context) "
+                             "with its start, length and its share of the critical path inside the replayed graph (CUPTI "
+                             "through torch.profiler), and exit")
     args = parser.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (run with --gpus 1)")
