@@ -229,6 +229,8 @@ def main(argv: list[str] | None = None) -> int:
         "rho": demand / capacity, "temperature": args.temperature, "seed": args.seed, "max_num_seqs": args.max_num_seqs,
         "max_num_batched_tokens": args.max_num_batched_tokens, "dtype": args.dtype, "started": started,
         "summary": summary, "cache_stats": asdict(llm.cache.stats()), "scheduler_stats": asdict(llm.scheduler.stats()),
+        "steps": {"all": llm.runner.steps, "from_graphs": llm.runner.graph_replays, "graphs_captured": llm.runner.graph_captures,
+                  "tokens_launched_kernel_by_kernel": llm.runner.eager_tokens},
         "waves": records, "final_histories": [len(h) for h in history],
         "final_history_digests": [hashlib.sha256(repr(h).encode()).hexdigest()[:16] for h in history],
     }

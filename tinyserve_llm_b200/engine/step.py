@@ -177,7 +177,10 @@ class StepRunner:
         self.max_graphs = max_graphs
         self._graph_pool = None                          # the graphs' intermediates share one memory pool
         self.last_graph: _StepGraph | None = None
-        self.graph_replays = 0
+        self.steps = 0                                   # steps run so far, of which ...
+        self.graph_replays = 0                           # ... from a graph (the step that captured one included) ...
+        self.graph_captures = 0                          # ... and how many graphs were captured; the rest was launched kernel by kernel
+        self.eager_tokens = 0                            # tokens of the steps launched kernel by kernel
 
     # ------------------------------------------------------------------ packing
     def _validate(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> None:
@@ -347,6 +350,7 @@ class StepRunner:
         """
         self._validate(entries, device_tokens)
         self.model.rt.ops.check_device_errors()      # a bounded wait that ran out in an earlier step (host-visible word)
+        self.steps += 1
         shape = self.graph_shape(entries) if self.cuda_graphs else None
         if shape is not None:
             captured = self._graphs.pop(shape, None)
@@ -361,6 +365,7 @@ class StepRunner:
                 self._met.clear()
             self._met[shape] = met
         ctx = self._pack(entries)
+        self.eager_tokens += ctx.num_tokens
         if device_tokens is not None:
             self.model.rt.ops.feed_tokens(ctx.token_ids, device_tokens)
         x, residual = self.model.forward(ctx)
@@ -458,6 +463,7 @@ class StepRunner:
             logits = self.model.logits(x, residual, ctx.rows, out=out)
         launches = ops.launches - before
         captured = _StepGraph(graph, index_buffer, logits, shape, launches)
+        self.graph_captures += 1
         while len(self._graphs) >= self.max_graphs:
             self._graphs.pop(next(iter(self._graphs)))
         self._graphs[shape] = captured
