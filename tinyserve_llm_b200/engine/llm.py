@@ -171,7 +171,19 @@ class LLM:
         sampler.sample_async(logits, [1.0] * seqs, [(i, 0, 0) for i in range(seqs)]).wait()
         torch.cuda.synchronize(device)
         step_peak = torch.cuda.max_memory_allocated(device) - baseline
-        del logits, eager, sampler
+        del logits, sampler
+        for e in entries:
+            manager.commit(e.seq_id, each)
+            manager.extend(e.seq_id, [0])
+        # One decode step for every batch size a graph will be captured for, beyond those the engine's own product
+        # serves: the library picks and loads its kernels per row count at first use (tens to hundreds of
+        # milliseconds), which would otherwise fall on the first step of that size while requests wait.
+        rows = 2 * self.model.rt.ops.skinny_max_rows
+        while rows <= StepRunner.bucket(seqs):
+            eager.step([StepEntry(i, [0], [0]) for i in range(min(rows, seqs))])
+            rows *= 2
+        torch.cuda.synchronize(device)
+        del eager
         graphs_held = 0
         if cuda_graphs and self.model.graph_safe:
             torch.cuda.empty_cache()
@@ -179,9 +191,6 @@ class LLM:
             widest = [-(-cfg.max_model_len // page)] * len(manager.pools)
             replayed = StepRunner(self.model, manager, storage, max_model_len=cfg.max_model_len,
                                   max_decode_batch=cfg.max_num_seqs, table_pages=widest)
-            for e in entries:
-                manager.commit(e.seq_id, each)
-                manager.extend(e.seq_id, [0])
             widest_tables = tuple(replayed._graph_widths)
             batch = StepRunner.bucket(seqs)
             replayed._capture([StepEntry(i, [0], [0]) for i in range(seqs)], StepShape(batch, batch, 0, 1, True, widest_tables))
