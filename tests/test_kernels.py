@@ -298,12 +298,17 @@ def test_tensor_core_attention_on_long_batches(ops, hd, g):
         torch.testing.assert_close(got.view(T, -1), same, **tol(torch.bfloat16, 2))
 
 
-@pytest.mark.parametrize("hd, g, page", [(64, 4, 256), (128, 2, 64)])
-def test_decode_attention_over_many_splits(ops, hd, g, page):
-    """Contexts of 17, 20 and 36 decode splits (the combination kernel takes 16 at a time), beside a first token."""
+@pytest.mark.parametrize("hd, g, page, ctx_lens, far", [(64, 4, 256, [4097, 9000, 5000, 1], 4100), (128, 2, 64, [4097, 9000, 5000, 1], 4100),
+                                                        (64, 4, 256, [4097, 131000, 5000, 1], 70001)],
+                         ids=["head64", "head128", "131000-tokens"])
+def test_decode_attention_over_many_splits(ops, hd, g, page, ctx_lens, far):
+    """
+    Contexts of 17, 20 and 36 decode splits (the combination kernel takes 16 at a time), beside a first token; and one
+    of 131,000 tokens (512 splits), about the longest a Llama 3.2 model takes.  One query is made to attend to a far
+    key above all.
+    """
     nkv = 2
     nh = nkv * g
-    ctx_lens = [4097, 9000, 5000, 1]
     q_lens = [1, 1, 1, 1]
     ctx = make_ctx(q_lens, ctx_lens)
     tables, at = [], 0
@@ -321,7 +326,7 @@ def test_decode_attention_over_many_splits(ops, hd, g, page):
             binding.k_pool[table[i], 0, :, :n] = keys[s][i * page:i * page + n].transpose(0, 1).to(DEV)
             binding.v_pool[table[i], 0, :, :n] = values[s][i * page:i * page + n].transpose(0, 1).to(DEV)
     qkv = rand((4, (nh + 2 * nkv) * hd), torch.bfloat16, 13)
-    qkv[1, :hd] = (keys[1][4100, 0].float() * 3).to(torch.bfloat16)      # request 1, head 0 attends to a key in its seventeenth split
+    qkv[1, :hd] = (keys[1][far, 0].float() * 3).to(torch.bfloat16)       # request 1, head 0 attends to a key in its seventeenth split or further
     scale = hd ** -0.5
     got = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0).cpu().double().view(4, nh, hd)
     want = torch.zeros_like(got)
@@ -532,6 +537,42 @@ def test_tcgen05_prompt_attention(ops, nh, nkv, page, hd):
     finally:
         ops.tcgen05_attention = True
     torch.testing.assert_close(got, legacy, **tol(torch.bfloat16, 2))
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_tcgen05_prompt_attention_behind_a_hundred_thousand_cached_tokens(ops, hd):
+    """
+    A portion of 130 tokens at the end of a context of 100,003: some 800 key tiles per query tile, 391 pages, the
+    last one partly filled.  One query attends to a key 88,000 tokens back above all.
+    """
+    if not ops.tcgen05_attention:
+        pytest.skip("TINYSERVE_B200_PREFILL=mma keeps prompt attention off the tcgen05 kernel in this run")
+    nh, nkv, page, c, n = 4, 1, 256, 100003, 130
+    pages = -(-c // page)
+    ctx = make_ctx([n], [c])
+    binding = make_binding(pages + 1, 1, nkv, page, hd, torch.bfloat16, [list(range(pages - 1, -1, -1))])
+    keys, values = rand((c, nkv, hd), torch.bfloat16, 80), rand((c, nkv, hd), torch.bfloat16, 81)
+    table = binding.block_table[0].tolist()
+    for i in range(pages):
+        m = min(page, c - i * page)
+        binding.k_pool[table[i], 0, :, :m] = keys[i * page:i * page + m].transpose(0, 1).to(DEV)
+        binding.v_pool[table[i], 0, :, :m] = values[i * page:i * page + m].transpose(0, 1).to(DEV)
+    qkv = rand((n, (nh + 2 * nkv) * hd), torch.bfloat16, 82)
+    qkv[7, hd:2 * hd] = (keys[12345, 0].float() * 3).to(torch.bfloat16)      # token 7, head 1
+    scale = hd ** -0.5
+    got = ops.paged_attention(qkv.to(DEV), ctx, binding, nh, nkv, hd, scale, 0).cpu().double().view(n, nh, hd)
+    torch.cuda.synchronize()
+    ops.check_device_errors()
+    q = qkv[:, : nh * hd].view(n, nh, hd).double()
+    k, v = keys[:, 0].double(), values[:, 0].double()
+    seen = torch.arange(c)[None, :] <= (c - n + torch.arange(n))[:, None]          # [n, c]: causal, bottom-right aligned
+    want = torch.zeros_like(got)
+    for h in range(nh):
+        scores = (q[:, h] @ k.T * scale).masked_fill(~seen, float("-inf"))
+        want[:, h] = plain.rnd(torch.softmax(scores, dim=1), "bfloat16") @ v
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got, plain.rnd(want, "bfloat16"), **tol(torch.bfloat16, 2))
+    assert torch.softmax((q[7, 1] @ k.T * scale)[: c - n + 8], dim=0)[12345] > 0.5    # the case is what it says
 
 
 @pytest.mark.parametrize("hd", [64, 128])

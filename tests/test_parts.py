@@ -37,12 +37,19 @@ def llama_parts(raw):
     return spec, spec.blocks[0]
 
 
-@pytest.mark.parametrize("raw", [TINY_B, TINY_C])
+# Llama 3.2 1B's rotary settings on a small model: a table of 131,072 positions, scaled past a window of 8,192
+LONG_ROPE = dict(TINY_B, head_dim=64, max_position_embeddings=131072, rope_theta=500000.0,
+                 rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                               "original_max_position_embeddings": 8192})
+
+
+@pytest.mark.parametrize("raw", [TINY_B, TINY_C, LONG_ROPE], ids=["b", "c", "llama-3.2-1b-rope"])
 def test_rotary_table_equals_the_plain_angles(raw):
     from tinyserve_llm_b200.parts.base import part_class
     _, block = llama_parts(raw)
     rotary = part_class("position", block.mixer.position)(block.mixer.position, {}, runtime(torch.float32))
-    positions = torch.tensor([0, 1, 63, 64, 65, raw["max_position_embeddings"] - 1])
+    last = raw["max_position_embeddings"] - 1
+    positions = torch.tensor(sorted({0, 1, 63, 64, 65, last // 16, last // 16 + 1, last // 2 + 1, last}))
     cos, sin = plain.rope_cos_sin(raw, positions)
     half = block.mixer.head_dim // 2
     table = rotary.table.cpu()[positions]
