@@ -470,9 +470,12 @@ def test_linear_with_swiglu_epilogue(ops, m, inter, k):
 
 
 @pytest.mark.parametrize("m, n, k", [(128, 128, 64), (1, 16, 8), (100, 200, 72), (130, 130, 136), (300, 1000, 192),
-                                      (2048, 3072, 2048), (257, 4096, 520), (64, 2048, 8192)])
+                                      (2048, 3072, 2048), (257, 4096, 520), (64, 2048, 8192), (1300, 5000, 200), (2048, 2048, 8192)])
 def test_tcgen05_matrix_product(ops, m, n, k):
-    """TMA-fed tcgen05 product: tiles that run over the edges of M, N and K, narrow and wide tile shapes."""
+    """
+    TMA-fed tcgen05 product: tiles that run over the edges of M, N and K, narrow and wide tile shapes, and (the large
+    ones) two CTAs on a tile of 256 x 256.
+    """
     x, w = rand((m, k), torch.bfloat16, 5), rand((n, k), torch.bfloat16, 6, 0.05)
     want = x.double() @ w.double().T
     scale = want.abs().max().item()
@@ -484,7 +487,8 @@ def test_tcgen05_matrix_product(ops, m, n, k):
     ops.check_device_errors()
 
 
-@pytest.mark.parametrize("m, inter, k", [(33, 64, 64), (100, 176, 72), (64, 8192, 2048), (2048, 8192, 2048), (300, 500, 192)])
+@pytest.mark.parametrize("m, inter, k", [(33, 64, 64), (100, 176, 72), (64, 8192, 2048), (2048, 8192, 2048), (300, 500, 192),
+                                         (1300, 2500, 136)])
 def test_tcgen05_product_with_swiglu_epilogue(ops, m, inter, k):
     x, w = rand((m, k), torch.bfloat16, 7), rand((2 * inter, k), torch.bfloat16, 8, 0.2)
     gate_up = plain.rnd(x.double() @ w.double().T, "bfloat16")
@@ -633,7 +637,7 @@ def test_environment_switches(ops, monkeypatch):
         for name in ("TINYSERVE_B200_CHAINING", "TINYSERVE_B200_PREFILL", "TINYSERVE_B200_SWIGLU_ROWS"):
             monkeypatch.delenv(name)
         defaults = Ops(ops.lib_path)
-        assert defaults.chaining and defaults.tcgen05_attention and defaults.tcgen05_swiglu_min_rows == 1408
+        assert defaults.chaining and defaults.tcgen05_attention and defaults.tcgen05_swiglu_min_rows == 512
         chained = chain(defaults)
     finally:
         ops.set_chaining(as_found)

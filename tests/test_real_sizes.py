@@ -1,7 +1,7 @@
 """
 Replay at the layer sizes of Llama 3.2 1B (two layers of its sixteen), float32 and bfloat16, against
 the plain implementation: the routes only these sizes take (256-token pages, the tcgen05 gate/up
-product from 1,408 rows, the library product from 33 rows, the vocabulary projection over 128,256
+product from 512 rows, the library product from 33 rows, the vocabulary projection over 128,256
 columns with float32 output, the tcgen05 prompt attention, rotary scaling with factor 32 over an
 8,192-token window) run inside the whole model here, not only as kernels alone.
 """

@@ -35,6 +35,7 @@ _SIGNATURES = {
     "ts_feed_tokens": ("int", "pipip"),
     "ts_gemm_tcgen05_supported": ("int", "ppiiil"),
     "ts_gemm_tcgen05": ("int", "pppiiilliipp"),
+    "ts_gemm_tcgen05_set_pairing": ("void", "i"),
     "ts_last_error": ("const char*", ""),
     "ts_abi_version": ("int", ""),
     "ts_set_chaining": ("void", "i"),
@@ -127,9 +128,10 @@ class Ops:
         # TINYSERVE_B200_PREFILL=mma keeps prompt attention on the mma.sync kernel (the tcgen05 one is the default)
         self.tcgen05_attention = os.environ.get("TINYSERVE_B200_PREFILL", "tcgen05") != "mma"
         # From this many rows of x the gate/up product runs on the engine's tcgen05 kernel with SwiGLU in its
-        # epilogue (10 to 20 % faster than the library product plus an activation kernel from 1,536 rows on a B200);
-        # below it the library product wins, whose tiles fit a few row tiles better.
-        self.tcgen05_swiglu_min_rows = int(os.environ.get("TINYSERVE_B200_SWIGLU_ROWS", "1408"))
+        # epilogue: measured on a B200 against the library product plus an activation kernel, it is 8 to 13 % faster
+        # from 512 rows on with Llama 3.2 1B's sizes (3B and 3.1 8B: the same or faster), and slower between 257 and
+        # about 450 rows, where three row tiles fit the SMs badly.
+        self.tcgen05_swiglu_min_rows = int(os.environ.get("TINYSERVE_B200_SWIGLU_ROWS", "512"))
         # up to this many rows the gate/up product with SwiGLU runs on the decode product (measured on a B200 with Llama
         # 3.2 1B's sizes, whole decode steps: 4 to 6 % faster than the library product plus the activation kernel at 12,
         # 16, 24 and 32 rows, since the weights go through the cp.async ring)
