@@ -95,7 +95,7 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t 
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {      // r: 32 registers (indices known at compile time)
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -219,75 +219,76 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             const uint32_t lane_addr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
             if (EPI == EPI_SWIGLU) {
                 __nv_bfloat16* out = (__nv_bfloat16*)p.y + (long long)row * p.ldy + n0;
-#pragma unroll 1
-                for (int c = side * (BN / 4); c < (side + 1) * (BN / 4); c += 32) {
-                    uint32_t gate[32], up[32];
-                    tmem_ld32(lane_addr + c, gate);
-                    tmem_ld32(lane_addr + BN / 2 + c, up);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + 32 >= (side + 1) * (BN / 4)) {   // this warp's share of the accumulator has been read: hand it back
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tmem_empty_bar[buf])) : "memory");
-                    }
-                    if (row < p.M) {
-                        const bool whole = n0 + c + 32 <= p.inter && (((uintptr_t)(out + c)) & 15) == 0;
+                // the warp's whole share of the accumulator into registers at once, so that the accumulator goes back
+                // to the MMAs before the arithmetic and the stores, not after them
+                constexpr int SHARE = BN / 4;
+                const int c0 = side * SHARE;
+                uint32_t gate[SHARE], up[SHARE];
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            float v[8];
+                for (int cc = 0; cc < SHARE; cc += 32) {
+                    tmem_ld32(lane_addr + c0 + cc, gate + cc);
+                    tmem_ld32(lane_addr + BN / 2 + c0 + cc, up + cc);
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tmem_empty_bar[buf])) : "memory");
+                if (row < p.M) {
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const float g = round_to<__nv_bfloat16>(__uint_as_float(gate[j + e]));
-                                const float u = round_to<__nv_bfloat16>(__uint_as_float(up[j + e]));
-                                v[e] = round_to<__nv_bfloat16>(g / (1.f + __expf(-g))) * u;
-                            }
-                            if (whole) {
-                                uint4 packed;
-                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+                    for (int j = 0; j < SHARE; j += 8) {
+                        const int c = c0 + j;
+                        float v[8];
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                                *reinterpret_cast<uint4*>(out + c + j) = packed;
-                            } else {
+                        for (int e = 0; e < 8; ++e) {
+                            const float g = round_to<__nv_bfloat16>(__uint_as_float(gate[j + e]));
+                            const float u = round_to<__nv_bfloat16>(__uint_as_float(up[j + e]));
+                            v[e] = round_to<__nv_bfloat16>(__fdividef(g, 1.f + __expf(-g))) * u;
+                        }
+                        if (n0 + c + 8 <= p.inter && (((uintptr_t)(out + c)) & 15) == 0) {
+                            uint4 packed;
+                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-                                for (int e = 0; e < 8; ++e)
-                                    if (n0 + c + j + e < p.inter) out[c + j + e] = __float2bfloat16_rn(v[e]);
-                            }
+                            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                            *reinterpret_cast<uint4*>(out + c) = packed;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (n0 + c + e < p.inter) out[c + e] = __float2bfloat16_rn(v[e]);
                         }
                     }
                 }
             } else {
-#pragma unroll 1
-                for (int c = side * (BN / 2); c < (side + 1) * (BN / 2); c += 32) {
-                    uint32_t acc[32];
-                    tmem_ld32(lane_addr + c, acc);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + 32 >= (side + 1) * (BN / 2)) {
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tmem_empty_bar[buf])) : "memory");
-                    }
-                    if (row < p.M) {
+                constexpr int SHARE = BN / 2;
+                const int c0 = side * SHARE;
+                uint32_t acc[SHARE];
+#pragma unroll
+                for (int cc = 0; cc < SHARE; cc += 32) tmem_ld32(lane_addr + c0 + cc, acc + cc);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tmem_empty_bar[buf])) : "memory");
+                if (row < p.M) {
+#pragma unroll
+                    for (int j = 0; j < SHARE; j += 8) {
+                        const int c = c0 + j;
                         if (p.out_f32) {
                             float* out = (float*)p.y + (long long)row * p.ldy + n0 + c;
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (n0 + c + j < p.N) out[j] = __uint_as_float(acc[j]);
+                            for (int e = 0; e < 8; ++e)
+                                if (n0 + c + e < p.N) out[e] = __uint_as_float(acc[j + e]);
                         } else {
                             __nv_bfloat16* out = (__nv_bfloat16*)p.y + (long long)row * p.ldy + n0 + c;
-                            if (n0 + c + 32 <= p.N && (((uintptr_t)out) & 15) == 0) {
+                            if (n0 + c + 8 <= p.N && (((uintptr_t)out) & 15) == 0) {
+                                uint4 v;
+                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-                                for (int j = 0; j < 32; j += 8) {
-                                    uint4 v;
-                                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e)
-                                        h[e] = __floats2bfloat162_rn(__uint_as_float(acc[j + 2 * e]), __uint_as_float(acc[j + 2 * e + 1]));
-                                    *reinterpret_cast<uint4*>(out + j) = v;
-                                }
+                                for (int e = 0; e < 4; ++e)
+                                    h[e] = __floats2bfloat162_rn(__uint_as_float(acc[j + 2 * e]), __uint_as_float(acc[j + 2 * e + 1]));
+                                *reinterpret_cast<uint4*>(out) = v;
                             } else {
 #pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (n0 + c + j < p.N) out[j] = __float2bfloat16_rn(__uint_as_float(acc[j]));
+                                for (int e = 0; e < 8; ++e)
+                                    if (n0 + c + e < p.N) out[e] = __float2bfloat16_rn(__uint_as_float(acc[j + e]));
                             }
                         }
                     }
@@ -453,75 +454,76 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_pair_kernel(const __grid
             const uint32_t drained = in_first_cta(&tmem_empty_bar[buf]);
             if (EPI == EPI_SWIGLU) {
                 __nv_bfloat16* out = (__nv_bfloat16*)p.y + (long long)row * p.ldy + n0;
-#pragma unroll 1
-                for (int c = side * (BN / 4); c < (side + 1) * (BN / 4); c += 32) {
-                    uint32_t gate[32], up[32];
-                    tmem_ld32(lane_addr + c, gate);
-                    tmem_ld32(lane_addr + BN / 2 + c, up);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + 32 >= (side + 1) * (BN / 4)) {   // this warp's share of the accumulator has been read: hand it back
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_remote(drained);
-                    }
-                    if (row < p.M) {
-                        const bool whole = n0 + c + 32 <= p.inter && (((uintptr_t)(out + c)) & 15) == 0;
+                // the warp's whole share of the accumulator into registers at once, so that the accumulator goes back
+                // to the MMAs before the arithmetic and the stores, not after them
+                constexpr int SHARE = BN / 4;
+                const int c0 = side * SHARE;
+                uint32_t gate[SHARE], up[SHARE];
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            float v[8];
+                for (int cc = 0; cc < SHARE; cc += 32) {
+                    tmem_ld32(lane_addr + c0 + cc, gate + cc);
+                    tmem_ld32(lane_addr + BN / 2 + c0 + cc, up + cc);
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(drained);
+                if (row < p.M) {
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const float g = round_to<__nv_bfloat16>(__uint_as_float(gate[j + e]));
-                                const float u = round_to<__nv_bfloat16>(__uint_as_float(up[j + e]));
-                                v[e] = round_to<__nv_bfloat16>(g / (1.f + __expf(-g))) * u;
-                            }
-                            if (whole) {
-                                uint4 packed;
-                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+                    for (int j = 0; j < SHARE; j += 8) {
+                        const int c = c0 + j;
+                        float v[8];
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                                *reinterpret_cast<uint4*>(out + c + j) = packed;
-                            } else {
+                        for (int e = 0; e < 8; ++e) {
+                            const float g = round_to<__nv_bfloat16>(__uint_as_float(gate[j + e]));
+                            const float u = round_to<__nv_bfloat16>(__uint_as_float(up[j + e]));
+                            v[e] = round_to<__nv_bfloat16>(__fdividef(g, 1.f + __expf(-g))) * u;
+                        }
+                        if (n0 + c + 8 <= p.inter && (((uintptr_t)(out + c)) & 15) == 0) {
+                            uint4 packed;
+                            __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-                                for (int e = 0; e < 8; ++e)
-                                    if (n0 + c + j + e < p.inter) out[c + j + e] = __float2bfloat16_rn(v[e]);
-                            }
+                            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                            *reinterpret_cast<uint4*>(out + c) = packed;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (n0 + c + e < p.inter) out[c + e] = __float2bfloat16_rn(v[e]);
                         }
                     }
                 }
             } else {
-#pragma unroll 1
-                for (int c = side * (BN / 2); c < (side + 1) * (BN / 2); c += 32) {
-                    uint32_t acc[32];
-                    tmem_ld32(lane_addr + c, acc);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (c + 32 >= (side + 1) * (BN / 2)) {
-                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive_remote(drained);
-                    }
-                    if (row < p.M) {
+                constexpr int SHARE = BN / 2;
+                const int c0 = side * SHARE;
+                uint32_t acc[SHARE];
+#pragma unroll
+                for (int cc = 0; cc < SHARE; cc += 32) tmem_ld32(lane_addr + c0 + cc, acc + cc);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(drained);
+                if (row < p.M) {
+#pragma unroll
+                    for (int j = 0; j < SHARE; j += 8) {
+                        const int c = c0 + j;
                         if (p.out_f32) {
                             float* out = (float*)p.y + (long long)row * p.ldy + n0 + c;
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (n0 + c + j < p.N) out[j] = __uint_as_float(acc[j]);
+                            for (int e = 0; e < 8; ++e)
+                                if (n0 + c + e < p.N) out[e] = __uint_as_float(acc[j + e]);
                         } else {
                             __nv_bfloat16* out = (__nv_bfloat16*)p.y + (long long)row * p.ldy + n0 + c;
-                            if (n0 + c + 32 <= p.N && (((uintptr_t)out) & 15) == 0) {
+                            if (n0 + c + 8 <= p.N && (((uintptr_t)out) & 15) == 0) {
+                                uint4 v;
+                                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-                                for (int j = 0; j < 32; j += 8) {
-                                    uint4 v;
-                                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e)
-                                        h[e] = __floats2bfloat162_rn(__uint_as_float(acc[j + 2 * e]), __uint_as_float(acc[j + 2 * e + 1]));
-                                    *reinterpret_cast<uint4*>(out + j) = v;
-                                }
+                                for (int e = 0; e < 4; ++e)
+                                    h[e] = __floats2bfloat162_rn(__uint_as_float(acc[j + 2 * e]), __uint_as_float(acc[j + 2 * e + 1]));
+                                *reinterpret_cast<uint4*>(out) = v;
                             } else {
 #pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (n0 + c + j < p.N) out[j] = __float2bfloat16_rn(__uint_as_float(acc[j]));
+                                for (int e = 0; e < 8; ++e)
+                                    if (n0 + c + e < p.N) out[e] = __float2bfloat16_rn(__uint_as_float(acc[j + e]));
                             }
                         }
                     }
