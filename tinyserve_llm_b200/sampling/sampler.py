@@ -75,6 +75,7 @@ class Sampler:
             seed = int.from_bytes(__import__("os").urandom(7), "little")
         self.seed = int(seed)
         self._results: list[torch.Tensor | None] = [None] * self.SLOTS
+        self._inputs: list[torch.Tensor | None] = [None] * self.SLOTS     # pinned too: temperatures and keys on their way up
         self._turn = 0
 
     def sample(self, logits: torch.Tensor, temperatures: Sequence[float], draws: Sequence[tuple[int, int, int]],
@@ -98,13 +99,18 @@ class Sampler:
         temps = np.asarray(temperatures, dtype=np.float32)
         keys = draw_keys(self.seed, draws)
         keys[temps <= 0] = 0                               # greedy rows draw nothing
-        packed = np.concatenate((temps.view(np.int32), keys.reshape(-1)))
-        dev = torch.from_numpy(packed).to(self.device, non_blocking=True)                         # one small copy
+        slot = self._turn
+        self._turn = (slot + 1) % self.SLOTS
+        staged = self._inputs[slot]                        # its last copy has run: that step's result has been read since
+        if staged is None or staged.numel() < 3 * count:
+            staged = self._inputs[slot] = torch.empty(max(3 * count, 192), dtype=torch.int32).pin_memory()
+        packed = staged.numpy()
+        packed[:count] = temps.view(np.int32)
+        packed[count:3 * count] = keys.reshape(-1)
+        dev = staged[:3 * count].to(self.device, non_blocking=True)                                # one small copy
         temps_dev = dev[:count].view(torch.float32)
         keys_dev = dev[count:].view(count, 2)
         tokens = self.ops.sample(logits.contiguous(), temps_dev, keys_dev)
-        slot = self._turn
-        self._turn = (slot + 1) % self.SLOTS
         host = self._results[slot]
         if host is None or host.numel() < count:
             host = self._results[slot] = torch.empty(max(count, 64), dtype=torch.int32).pin_memory()
